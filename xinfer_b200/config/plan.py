@@ -129,6 +129,15 @@ class AttentionSpec(PartSpec):
     # tensor names of the q, k, v, output (and talk) matrices after the part's prefix; None: the
     # "q_proj.weight" family
     names: Optional[Tuple[str, ...]] = None
+    # q, k and v have biases: the matrix's name with this suffix (None: no biases)
+    bias_suffix: Optional[str] = None
+    # names of the q and k norm weights after the prefix (None: "q_norm.weight", "k_norm.weight")
+    qk_norm_names: Optional[Tuple[str, str]] = None
+    # query temperature (coef, every): the query at position p is multiplied by
+    # 1 + coef * ln(floor((p + 1) / every) + 1), after its norm and rotation
+    q_temp: Optional[Tuple[float, int]] = None
+    # the concatenated heads are multiplied by sigmoid(W_g h) before the output projection; the name of W_g
+    gate_name: Optional[str] = None
 
     @property
     def value_dim(self) -> int:
@@ -177,14 +186,66 @@ class GatedRecurrenceSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class SelectiveStateSpec(PartSpec):
+    """A state-space mixer in the form of Mamba-2: ``heads`` heads of ``head_dim`` channels, a state of ``state``
+    rows per head, input and output maps B and C shared by the heads of one of ``groups`` groups.  One input
+    projection gives ``[z | x | B | C | dt]``; x, B and C pass a causal convolution of ``conv`` taps per channel
+    (with a bias) and SiLU; dt = softplus(dt + dt_bias); per head S <- exp(-exp(A_log) dt) S + dt B x^T and
+    y = S^T C + D x; y * silu(z) is RMS-normed in ``norm_groups`` equal parts (``eps``) with one weight over all
+    channels, then projected out.  ``names``: the input projection, the convolution (its bias: that name plus
+    ``.b``), dt_bias, A_log, D, the norm and the output projection after the prefix."""
+
+    hidden: int = 0
+    heads: int = 0
+    head_dim: int = 0
+    state: int = 0
+    groups: int = 1
+    conv: int = 4
+    norm_groups: int = 1
+    eps: float = 1e-6
+    names: Tuple[str, ...] = ("in", "conv", "dt_bias", "A_log", "D", "norm", "o")
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec(PartSpec):
+    """The gated delta rule: ``heads`` value heads of ``v_head_dim`` channels over ``kv_heads`` query/key heads of
+    ``head_dim``.  q, k, v pass a causal convolution of ``conv`` taps per channel (no bias) and SiLU; q and k become
+    unit vectors per head (``unit_eps`` under the root), q also times head_dim^-1/2; beta = sigmoid(W_b h) per head;
+    a decay per head and key channel, g = exp(-exp(A_log_h) softplus(W_a2 (W_a1 h) + dt_bias)); per head
+    S <- diag(g) S, u = beta (v - S^T k), S <- S + k u^T, o = S^T q; o is RMS-normed per head (``eps``) with one
+    weight shared by the heads, times sigmoid(W_g2 (W_g1 h)), then projected out.  ``decay_rank`` / ``gate_rank``:
+    the inner sizes of the two low-rank maps; None: whatever the tensors' shapes say (the random-weights mode then
+    draws ``DEFAULT_RANK``)."""
+
+    hidden: int = 0
+    heads: int = 0
+    kv_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    conv: int = 4
+    eps: float = 1e-6
+    unit_eps: float = 1e-6
+    decay_rank: Optional[int] = None
+    gate_rank: Optional[int] = None
+
+    DEFAULT_RANK = 16
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec(PartSpec):
-    """Two mixers that read the same input; the result is left_scale * left + right_scale * right."""
+    """Two mixers that read the same input; the result is left_scale * left + right_scale * right.
+    ``out_norms`` = (left name, right name): each mixer's result (after its own output projection) is first
+    RMS-normed over the model width with a learned weight of that name after the prefix (``out_norm_eps``; the
+    weight enters as ``out_norm_offset + w``)."""
 
     hidden: int = 0
     left: Optional[PartSpec] = None
     right: Optional[PartSpec] = None
     left_scale: float = 1.0
     right_scale: float = 1.0
+    out_norms: Optional[Tuple[str, str]] = None
+    out_norm_eps: float = 1e-6
+    out_norm_offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -195,6 +256,23 @@ class FeedForwardSpec(PartSpec):
     eps: float = 1e-6      # of activations that norm (polynorm)
     # tensor names of the gate, up and down matrices after the part's prefix; None: the "gate_proj.weight" family
     names: Optional[Tuple[str, ...]] = None
+    # the three projections have biases: the matrix's name with this suffix (None: no biases)
+    bias_suffix: Optional[str] = None
+
+
+@dataclass(frozen=True)
+class TokenSideSpec(PartSpec):
+    """A layer's own input from the token ids: with e the ``dim`` columns from ``column`` of the row of a table
+    over token ids (``table``: the tensor's full name, shared by all layers, ``columns`` wide),
+    y = W_proj (gelu_tanh(W_gate x) * e).  ``names``: W_gate and W_proj after the prefix."""
+
+    hidden: int = 0
+    dim: int = 0
+    vocab: int = 0
+    table: str = ""
+    column: int = 0
+    columns: int = 0
+    names: Tuple[str, str] = ("gate", "proj")
 
 
 @dataclass(frozen=True)
@@ -217,7 +295,8 @@ class BlockOp:
 
     * ``op="norm"``: ``dst = norm(src)`` with the norm ``spec``;
     * ``op="mixer"`` / ``op="feed_forward"``: ``dst = part(src)`` with the part ``spec``;
-    * ``op="add"``: ``dst = dst + scale * src`` (no spec).
+    * ``op="add"``: ``dst = dst + scale * gain * src`` (no spec); ``gain`` names a learned vector over the
+      channels (its tensor name after the block's prefix; None: ones).
 
     ``name`` is the tensor-name piece between the block's prefix and the part's own tensor names;
     two operations with the same ``op`` and ``name`` are the same part (one set of weights).
@@ -232,6 +311,7 @@ class BlockOp:
     spec: Optional[PartSpec] = None
     name: str = ""
     scale: float = 1.0
+    gain: Optional[str] = None
 
 
 BLOCK_OPS = ("norm", "mixer", "feed_forward", "add")
@@ -279,8 +359,8 @@ class BlockSpec:
                     raise ValueError(f"{where}: an addition has no part")
                 if o.src == o.dst:
                     raise ValueError(f"{where}: adds '{o.src}' to itself")
-            elif o.scale != 1.0:
-                raise ValueError(f"{where}: only an addition has a scale")
+            elif o.scale != 1.0 or o.gain is not None:
+                raise ValueError(f"{where}: only an addition has a scale or a gain")
             else:
                 if o.spec is None:
                     raise ValueError(f"{where}: needs a part spec")
@@ -307,6 +387,17 @@ def pre_norm_block(prefix: str, norm_in: NormSpec, mixer: PartSpec, norm_post: N
         BlockOp("feed_forward", "h", "f", feed_forward, feed_forward_name),
         BlockOp("add", "f", "x"),
     ))
+
+
+@dataclass(frozen=True)
+class PairEmbeddingSpec:
+    """A table of ``buckets + 1`` rows added to the embedding: a token after ``prev`` takes row
+    ``(prev * mul_prev + token * mul_cur) mod buckets``, a sequence's first token the last row."""
+
+    name: str
+    buckets: int
+    mul_prev: int
+    mul_cur: int
 
 
 @dataclass(frozen=True)
@@ -340,6 +431,10 @@ class ModelPlan:
     logit_softcap: Optional[float] = None
     # the residual stream's dtype ("float32"); None = the engine's dtype
     residual_dtype: Optional[str] = None
+    # added to every token's embedding row: a row of a table over hashed (previous token, token) pairs, and a
+    # learned vector per position (the tensor's name; it has max_positions rows)
+    pair_embedding: Optional["PairEmbeddingSpec"] = None
+    position_table: Optional[str] = None
     # standard deviations used by the random-weights mode
     init_std: float = 0.02
     norm_init_std: float = 0.1
@@ -351,6 +446,8 @@ class ModelPlan:
             b.validate()
         if self.residual_dtype not in (None, "float32"):
             raise ValueError(f"residual_dtype must be None or 'float32', got {self.residual_dtype!r}")
+        if (self.pair_embedding is not None or self.position_table is not None) and self.residual_dtype != "float32":
+            raise ValueError("a pair embedding or a position table is summed into a float32 residual stream")
         if self.logit_softcap is not None and not (self.logit_softcap > 0):
             raise ValueError(f"logit_softcap must be positive, got {self.logit_softcap}")
         for pos, run in enumerate(self.runs):

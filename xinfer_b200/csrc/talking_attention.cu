@@ -19,6 +19,8 @@
 //   rotation of the first `rot` channels by position * inv_freq[pair]  (inv_freq absent: none);
 //     cos and sin are multiplied by rot_mag (1: a pure rotation)
 //   norm_mode 2: x <- x / rms(x) * w
+// `bias` (float32, laid out like a qkv row; absent: none) is added to q, k and v first.  With temp_every > 0 a
+// query at position p is multiplied, last of all, by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1).
 // q goes to q_out[t, h], k and v into their pages ([page, kv_head, slot, d] and [.., dv]).
 // One block per token, one warp per head at a time; the angles' cos/sin are formed once per token.
 // ------------------------------------------------------------------------------------------
@@ -57,7 +59,9 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
                                    const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                    const int* __restrict__ req_of_token, const int* __restrict__ block_table,
                                    int table_stride, int nh, int nkv, int d, int dv, int rot, int interleaved, int norm_mode,
-                                   int page_size, int num_pages, float eps, int write_kv, int vec4, float rot_mag, int* err) {
+                                   int page_size, int num_pages, float eps, int write_kv, int vec4, float rot_mag,
+                                   const float* __restrict__ bias, float temp_coef, int temp_every, long long row_len,
+                                   int* err) {
     extern __shared__ float sm[];
     const int half = rot / 2;
     float* cs = sm;                 // [half]
@@ -86,20 +90,28 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
             kv_row = (long long)page * nkv * page_size + (pos % page_size);
         }
     }
-    const size_t row_len = (size_t)(nh + nkv) * d + (size_t)nkv * dv;
-    const T* row = qkv + (size_t)t * row_len;
+    const T* row = qkv + (size_t)t * row_len;     // (a row may hold more behind its q, k and v)
+    // the query's temperature: it grows with the logarithm of the number of whole periods the sequence has seen
+    const float q_mul = temp_every > 0 ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f) : 1.f;
     for (int h = warp; h < nh + 2 * nkv; h += nwarps) {
-        if (h >= nh + nkv) {      // a value head: copy
+        if (h >= nh + nkv) {      // a value head: copy (plus its bias)
             if (kv_row < 0) continue;
             const int g = h - nh - nkv;
             const T* x = row + (size_t)(nh + nkv) * d + (size_t)g * dv;
+            const float* bv = bias ? bias + (size_t)(nh + nkv) * d + (size_t)g * dv : nullptr;
             T* dst = v_cache + (size_t)(kv_row + (long long)g * page_size) * dv;
             if (vec4) {
                 for (int i = lane * 4; i < dv; i += 128) {
                     float v[4];
                     load4<T>(x + i, v);
+                    if (bv) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) v[k] += bv[i + k];
+                    }
                     store4<T>(dst + i, v);
                 }
+            } else if (bv) {
+                for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(to_f32<T>(x[i]) + bv[i]);
             } else {
                 for (int i = lane; i < dv; i += 32) dst[i] = x[i];
             }
@@ -108,6 +120,8 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
         const bool is_q = h < nh;
         if (!is_q && kv_row < 0) continue;
         const T* x = row + (size_t)h * d;
+        const float* bh = bias ? bias + (size_t)h * d : nullptr;
+        const float om = is_q ? q_mul : 1.f;
         T* dst = is_q ? q_out + ((size_t)t * nh + h) * d
                       : k_cache + (size_t)(kv_row + (long long)(h - nh) * page_size) * d;
         const float* nw = is_q ? q_w : k_w;
@@ -118,13 +132,14 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
                 load4<T>(x + i, v);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
+                    if (bh) v[k] += bh[i + k];
                     xs[i + k] = v[k];
                     ss += v[k] * v[k];
                 }
             }
         } else {
             for (int i = lane; i < d; i += 32) {
-                const float v = to_f32<T>(x[i]);
+                const float v = to_f32<T>(x[i]) + (bh ? bh[i] : 0.f);
                 xs[i] = v;
                 ss += v * v;
             }
@@ -154,13 +169,13 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
             for (int i = lane * 4; i < d; i += 128) {
                 float v[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) v[k] = norm_mode == 2 ? xs[i + k] * inv * (nw ? nw[i + k] : 1.f) : xs[i + k];
+                for (int k = 0; k < 4; ++k) v[k] = (norm_mode == 2 ? xs[i + k] * inv * (nw ? nw[i + k] : 1.f) : xs[i + k]) * om;
                 store4<T>(dst + i, v);
             }
         } else if (norm_mode == 2) {
-            for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(xs[i] * inv * (nw ? nw[i] : 1.f));
+            for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(xs[i] * inv * (nw ? nw[i] : 1.f) * om);
         } else {
-            for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(xs[i]);
+            for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(xs[i] * om);
         }
         __syncwarp();
     }
@@ -169,7 +184,8 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
 XB_EXPORT int xb_qkv_prepare(int dtype, void* q_out, void* k_cache, void* v_cache, const void* qkv, const float* q_w,
                              const float* k_w, const float* inv_freq, const int* positions, const int* req_of_token,
                              const int* block_table, int table_stride, int tokens, int nh, int nkv, int d, int dv, int rot,
-                             int interleaved, int norm_mode, int page_size, int num_pages, float eps, int write_kv, float rot_mag, int* err,
+                             int interleaved, int norm_mode, int page_size, int num_pages, float eps, int write_kv, float rot_mag,
+                             const float* bias, float temp_coef, int temp_every, long long row_len, int* err,
                              cudaStream_t stream) {
     if (tokens <= 0) return 0;
     // a warp per head at a time: as many warps as a token has heads, up to 16
@@ -183,17 +199,18 @@ XB_EXPORT int xb_qkv_prepare(int dtype, void* q_out, void* k_cache, void* v_cach
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     // four elements per access where every head starts on such a boundary, in the rows and in the pages
     const size_t esz = dtype == XB_F32 ? 4 : 2;
-    const int vec4 = (d % 4 == 0 && dv % 4 == 0 &&
+    const int vec4 = (d % 4 == 0 && dv % 4 == 0 && row_len % 4 == 0 &&
                       !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & (4 * esz - 1))) ? 1 : 0;
     if (dtype == XB_F32)
         qkv_prepare_kernel<float><<<tokens, threads, smem, stream>>>(
             (float*)q_out, (float*)k_cache, (float*)v_cache, (const float*)qkv, q_w, k_w, inv_freq, positions, req_of_token,
-            block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode, page_size, num_pages, eps, write_kv, vec4, rot_mag, err);
+            block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode, page_size, num_pages, eps, write_kv, vec4, rot_mag,
+            bias, temp_coef, temp_every, row_len, err);
     else
         qkv_prepare_kernel<__nv_bfloat16><<<tokens, threads, smem, stream>>>(
             (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const __nv_bfloat16*)qkv, q_w, k_w,
             inv_freq, positions, req_of_token, block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode,
-            page_size, num_pages, eps, write_kv, vec4, rot_mag, err);
+            page_size, num_pages, eps, write_kv, vec4, rot_mag, bias, temp_coef, temp_every, row_len, err);
     return xb_launch_status();
 }
 

@@ -347,7 +347,10 @@ class ModelRunner:
                 continue
             self.layer_states.append({name: self.state.add(f"run{pos}.{name}", shape, dt)
                                       for name, (shape, dt) in need.items()})
-        self.has_state = any(s is not None for s in self.layer_states)
+        own = self.model.state_need_of_model()
+        if own:
+            self.model.bind_state({name: self.state.add(f"model.{name}", shape, dt) for name, (shape, dt) in own.items()})
+        self.has_state = any(s is not None for s in self.layer_states) or bool(own)
         # decode steps may be replayed from CUDA graphs when every part takes the step from device tensors
         self._graph_safe = self.model.graph_safe()
 

@@ -668,13 +668,25 @@ def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, block_table, t
 
 # ---- attention with talking heads and a sink; gated recurrence; polynomial activation; table experts ----
 def qkv_prepare(q_out, k_cache, v_cache, qkv, q_w, k_w, inv_freq, positions, req_of_token, block_table, table_stride,
-                nh, nkv, d, dv, rot, interleaved, norm_mode, eps, write_kv, err, rot_magnitude: float = 1.0):
+                nh, nkv, d, dv, rot, interleaved, norm_mode, eps, write_kv, err, rot_magnitude: float = 1.0, bias=None,
+                q_temp=None, row_len=None):
     """Per q/k head of the packed ``qkv`` rows ``[heads*d | kv_heads*d | kv_heads*dv]``: norm over the head
     (``norm_mode`` 1: before the rotation, 2: after it, 0: none; weight ``q_w`` / ``k_w`` or none), rotation of
     the first ``rot`` channels by ``position * inv_freq`` (float32 angles formed in the kernel; ``inv_freq`` None:
-    no rotation; cos and sin are multiplied by ``rot_magnitude``); q to ``q_out``, k and v into their pages."""
+    no rotation; cos and sin are multiplied by ``rot_magnitude``); q to ``q_out``, k and v into their pages.
+    ``bias`` (float32, as long as a ``qkv`` row) is added first of all.  ``q_temp`` = (coef, every): a query at
+    position p is multiplied, last of all, by ``1 + coef * ln(floor((p + 1) / every) + 1)``."""
     T = qkv.shape[0]
-    _need(qkv, "qkv", None, (T, (nh + nkv) * d + nkv * dv))
+    need_len = (nh + nkv) * d + nkv * dv
+    row_len = need_len if row_len is None else int(row_len)     # rows may hold more behind their q, k and v
+    if row_len < need_len:
+        raise KernelError(f"rows of {row_len} elements cannot hold q, k and v of {need_len}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, ((nh + nkv) * d + nkv * dv,))
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp is not None else (0.0, 0)
+    if q_temp is not None and every <= 0:
+        raise KernelError(f"the query temperature's period must be positive, got {every}")
+    _need(qkv, "qkv", None, (T, row_len))
     _need(q_out, "q_out", qkv.dtype, (T, nh, d))
     if write_kv:
         _need(k_cache, "k_cache", qkv.dtype, (None, nkv, None, d))
@@ -690,7 +702,8 @@ def qkv_prepare(q_out, k_cache, v_cache, qkv, q_w, k_w, inv_freq, positions, req
         dtype_code(qkv.dtype), q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache), qkv.data_ptr(), _ptr(q_w), _ptr(k_w),
         _ptr(inv_freq), positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), int(table_stride), T, nh, nkv,
         d, dv, int(rot if inv_freq is not None else 0), int(bool(interleaved)), int(norm_mode), page_size, num_pages,
-        float(eps), int(bool(write_kv)), float(rot_magnitude), err.data_ptr(), _stream()), "qkv_prepare")
+        float(eps), int(bool(write_kv)), float(rot_magnitude), _ptr(bias), coef, every, row_len, err.data_ptr(), _stream()),
+        "qkv_prepare")
 
 
 def attn_talking_tile(nh: int, d: int, dv: int, want: int) -> int:
@@ -964,3 +977,198 @@ def gemm_batched_plain(out, a, w):
     _ok(kernels_lib().xb_gemm_batched_plain(dtype_code(a.dtype), out.data_ptr(), a.data_ptr(), w.data_ptr(), B, M, N, K,
                                             a.stride(0), a.stride(1), w.stride(0), w.stride(1), w.stride(2), out.stride(0),
                                             out.stride(1), _stream()), "gemm_batched_plain")
+
+
+# ---- RMS norm with the residual arithmetic around it; biases --------------------------------------------------------
+def rms_chain(out, x, weight, eps, err, *, branch=None, branch_weight=None, branch_eps=0.0, branch_offset=0.0, gain=None,
+              branch_scale: float = 1.0, sum_out=None, rows=None, weight_offset: float = 0.0):
+    """One pass over rows of the float32 stream ``x``: s = x + branch_scale * gain * br, where br is the branch, or with
+    ``branch_weight`` its own RMS norm ``branch / rms(branch) * (branch_offset + branch_weight)``; ``sum_out`` receives s
+    (it may be x itself when no rows are gathered); ``out`` (either type; None: only the sum) receives
+    ``s / rms(s) * (weight_offset + weight)``, or s itself where ``weight`` is None."""
+    dim = x.shape[-1]
+    n = out.shape[0] if out is not None else x.shape[0]
+    _need(x, "x", torch.float32, (None, dim))
+    if out is not None:
+        _need(out, "out", None, (n, dim))
+    for name, t in (("weight", weight), ("branch_weight", branch_weight), ("gain", gain)):
+        if t is not None:
+            _need(t, name, torch.float32, (dim,))
+    if branch is not None:
+        _need(branch, "branch", None, tuple(x.shape))
+    elif branch_weight is not None or gain is not None:
+        raise KernelError("a branch norm or a gain needs a branch")
+    if sum_out is not None:
+        _need(sum_out, "sum_out", torch.float32, (n, dim))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() < n:
+            raise KernelError(f"rows holds {rows.numel()} entries for {n} output rows")
+    elif n != x.shape[0]:
+        raise KernelError(f"out has {n} rows, x has {x.shape[0]} and no row list was given")
+    _ok(kernels_lib().xb_rms_chain(dtype_code(branch.dtype) if branch is not None else F32,
+                                   dtype_code(out.dtype) if out is not None else F32, _ptr(out), _ptr(sum_out), x.data_ptr(),
+                                   _ptr(branch), _ptr(rows), _ptr(weight), _ptr(branch_weight), _ptr(gain), n, dim, x.shape[0],
+                                   float(eps), float(weight_offset), float(branch_eps), float(branch_offset),
+                                   float(branch_scale), err.data_ptr(), _stream()), "rms_chain")
+
+
+def dual_rms_sum(out, left, right, w_left, w_right, eps, left_scale: float, right_scale: float, weight_offset: float = 0.0):
+    """out = left_scale * rms_norm(left; w_left) + right_scale * rms_norm(right; w_right), row by row."""
+    T, dim = left.shape
+    _need(left, "left", None, (T, dim))
+    _need(right, "right", left.dtype, (T, dim))
+    _need(out, "out", left.dtype, (T, dim))
+    _need(w_left, "w_left", torch.float32, (dim,))
+    _need(w_right, "w_right", torch.float32, (dim,))
+    _ok(kernels_lib().xb_dual_rms_sum(dtype_code(left.dtype), out.data_ptr(), left.data_ptr(), right.data_ptr(),
+                                      w_left.data_ptr(), w_right.data_ptr(), T, dim, float(eps), float(weight_offset),
+                                      float(left_scale), float(right_scale), _stream()), "dual_rms_sum")
+
+
+def add_bias(x, bias):
+    """x[t, :] += bias, in place."""
+    T, dim = x.shape
+    _need(x, "x", None, (T, dim))
+    _need(bias, "bias", torch.float32, (dim,))
+    _ok(kernels_lib().xb_add_bias(dtype_code(x.dtype), x.data_ptr(), bias.data_ptr(), T, dim, _stream()), "add_bias")
+
+
+def swiglu_bias(out, gate_up, bias, activation: str = "silu"):
+    """out[t, i] = act(gate_up[t, i] + bias[i]) * (gate_up[t, I + i] + bias[I + i])."""
+    T, two_i = gate_up.shape
+    _need(gate_up, "gate_up", None, (T, two_i))
+    _need(out, "out", None, (T, two_i // 2))
+    _need(bias, "bias", torch.float32, (two_i,))
+    _ok(kernels_lib().xb_swiglu_bias(dtype_code(gate_up.dtype), dtype_code(out.dtype), out.data_ptr(), gate_up.data_ptr(),
+                                     bias.data_ptr(), T, two_i // 2, ACTIVATIONS[activation], _stream()), "swiglu_bias")
+
+
+# ---- what is added to a token's embedding row; a layer's own table over token ids -----------------------------------
+def embed_sum(out, table, ids, err, *, sampled=None, scale=None, pair=None, pair_rule=None, pos_table=None, positions=None,
+              req_of_token=None, q_start=None, slots=None, prev_state=None):
+    """out[t] = table[id] * scale + pair[row] + pos_table[position] (float32).  ``pair_rule`` = (buckets, mul_prev,
+    mul_cur): row = (prev * mul_prev + id * mul_cur) mod buckets, where prev is the token before - the one before in
+    this step, or ``prev_state[slot]`` for a request's first token of the step - and row ``buckets`` at position 0.
+    Rows of padding tokens are zero."""
+    T, H = out.shape
+    _need(out, "out", torch.float32, (T, H))
+    _need(table, "table", None, (None, H))
+    for name, t in (("ids", ids), ("positions", positions), ("req_of_token", req_of_token), ("q_start", q_start), ("slots", slots)):
+        _need(t, name, torch.int32)
+    buckets = mp = mc = 0
+    if pair is not None:
+        buckets, mp, mc = (int(v) for v in pair_rule)
+        _need(pair, "pair", table.dtype, (buckets + 1, H))
+        _need(prev_state, "prev_state", torch.int32)
+    if pos_table is not None:
+        _need(pos_table, "pos_table", table.dtype, (None, H))
+    _ok(kernels_lib().xb_embed_sum(dtype_code(table.dtype), out.data_ptr(), table.data_ptr(), _ptr(pair), _ptr(pos_table),
+                                   ids.data_ptr(), _ptr(sampled), sampled.numel() if sampled is not None else 0,
+                                   positions.data_ptr(), req_of_token.data_ptr(), q_start.data_ptr(), slots.data_ptr(),
+                                   _ptr(prev_state), T, H, table.shape[0], buckets, mp, mc,
+                                   pos_table.shape[0] if pos_table is not None else 0, 1.0 if scale is None else float(scale),
+                                   err.data_ptr(), _stream()), "embed_sum")
+
+
+def prev_store(prev_state, ids, sampled, q_start, slots, num_entries):
+    """prev_state[slot] = the last token every entry brought in this step."""
+    _need(prev_state, "prev_state", torch.int32)
+    _ok(kernels_lib().xb_prev_store(prev_state.data_ptr(), ids.data_ptr(), _ptr(sampled),
+                                    sampled.numel() if sampled is not None else 0, q_start.data_ptr(), slots.data_ptr(),
+                                    int(num_entries), _stream()), "prev_store")
+
+
+def token_gate(out, u, table, col0, ids, sampled, req_of_token, err):
+    """out[t, j] = gelu_tanh(u[t, j]) * table[id, col0 + j]."""
+    T, dim = u.shape
+    _need(u, "u", None, (T, dim))
+    _need(out, "out", u.dtype, (T, dim))
+    _need(table, "table", u.dtype, (None, None))
+    if col0 < 0 or col0 + dim > table.shape[1]:
+        raise KernelError("the layer's columns lie outside the table")
+    _ok(kernels_lib().xb_token_gate(dtype_code(u.dtype), out.data_ptr(), u.data_ptr(), table.data_ptr(), table.shape[1], int(col0),
+                                    ids.data_ptr(), _ptr(sampled), sampled.numel() if sampled is not None else 0,
+                                    req_of_token.data_ptr(), T, dim, table.shape[0], err.data_ptr(), _stream()), "token_gate")
+
+
+# ---- short convolutions and recurrences with a matrix state ----------------------------------------------------------
+CONV_MAX_TAPS = 16
+
+
+def conv_silu(y, u, u_off, taps, bias, state, req_of_token, q_start, slots, num_entries):
+    """y[t, c] = silu(bias[c] + sum_j taps[c, j] * u[t - (K-1) + j, u_off + c]) per request, the K-1 inputs before a step's
+    first token taken from ``state`` ``[slots, K-1, C]`` (float32), which then receives the step's last K-1 inputs."""
+    T, C = y.shape
+    K = taps.shape[1]
+    _need(y, "y", None, (T, C))
+    _need(u, "u", torch.float32, (T, None))
+    _need(taps, "taps", torch.float32, (C, K))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (C,))
+    if u_off < 0 or u_off + C > u.shape[1]:
+        raise KernelError("the convolution's channels lie outside the rows")
+    if K > CONV_MAX_TAPS:
+        raise KernelError(f"a short convolution has at most {CONV_MAX_TAPS} taps, got {K}")
+    if K > 1:
+        _need(state, "state", torch.float32, (None, K - 1, C))
+    lib = kernels_lib()
+    _ok(lib.xb_conv_silu(dtype_code(y.dtype), y.data_ptr(), u.data_ptr(), u.shape[1], int(u_off), taps.data_ptr(), _ptr(bias),
+                         _ptr(state) if K > 1 else None, req_of_token.data_ptr(), q_start.data_ptr(), slots.data_ptr(), T, C, K,
+                         _stream()), "conv_silu")
+    if K > 1:
+        _ok(lib.xb_conv_state(state.data_ptr(), u.data_ptr(), u.shape[1], int(u_off), q_start.data_ptr(), slots.data_ptr(),
+                              int(num_entries), C, K, _stream()), "conv_state")
+
+
+def selective_scan(y, xbc, proj, dt_off, dt_bias, a_log, d_skip, state, q_start, slots, num_entries, heads, head_dim, n_state,
+                   groups):
+    """S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d_skip x per (request, head); ``xbc`` float32 rows
+    ``[x | B | C]``, dt = softplus(proj[:, dt_off + h] + dt_bias); ``state`` ``[slots, heads, n_state, head_dim]``."""
+    T = xbc.shape[0]
+    inner = heads * head_dim
+    _need(xbc, "xbc", torch.float32, (T, inner + 2 * groups * n_state))
+    _need(proj, "proj", torch.float32, (T, None))
+    _need(y, "y", torch.float32, (T, inner))
+    for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
+        _need(t, name, torch.float32, (heads,))
+    _need(state, "state", torch.float32, (None, heads, n_state, head_dim))
+    _ok(kernels_lib().xb_selective_scan(y.data_ptr(), xbc.data_ptr(), xbc.shape[1], proj.data_ptr(), proj.shape[1], int(dt_off),
+                                        dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(),
+                                        q_start.data_ptr(), slots.data_ptr(), int(num_entries), heads, head_dim, n_state, groups,
+                                        _stream()), "selective_scan")
+
+
+def delta_rule(o, qkv, proj, beta_off, ag, dt_bias, a_log, state, q_start, slots, num_entries, heads, kv_heads, d, dv,
+               unit_eps: float = 1e-6):
+    """The gated delta rule per (request, head): ``qkv`` float32 rows ``[q | k | v]`` (q and k per key head), beta =
+    sigmoid(proj[:, beta_off + h]), decay per (head, key channel) from the front of ``ag`` rows; ``state``
+    ``[slots, heads, d, dv]``; ``o`` ``[T, heads * dv]`` before its norm and gate."""
+    T = qkv.shape[0]
+    _need(qkv, "qkv", torch.float32, (T, 2 * kv_heads * d + heads * dv))
+    _need(proj, "proj", torch.float32, (T, None))
+    _need(ag, "ag", torch.float32, (T, None))
+    _need(o, "o", torch.float32, (T, heads * dv))
+    _need(dt_bias, "dt_bias", torch.float32, (heads * d,))
+    _need(a_log, "a_log", torch.float32, (heads,))
+    _need(state, "state", torch.float32, (None, heads, d, dv))
+    _ok(kernels_lib().xb_delta_rule(o.data_ptr(), qkv.data_ptr(), qkv.shape[1], proj.data_ptr(), proj.shape[1], int(beta_off),
+                                    ag.data_ptr(), ag.shape[1], dt_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(),
+                                    q_start.data_ptr(), slots.data_ptr(), int(num_entries), heads, kv_heads, d, dv,
+                                    float(unit_eps), _stream()), "delta_rule")
+
+
+def gated_head_norm(out, y, gate, g_off, weight, part, eps, gate_after: bool):
+    """Per token and group of ``part`` channels of ``y`` (float32): with ``gate_after`` False,
+    v = y * silu(gate), out = v / rms(v) * weight; with True, out = y / rms(y) * weight * sigmoid(gate).  ``gate`` is
+    the columns from ``g_off`` of float32 rows; ``weight`` repeats every ``weight.numel()`` channels."""
+    T, W = y.shape
+    _need(y, "y", torch.float32, (T, W))
+    _need(out, "out", None, (T, W))
+    _need(gate, "gate", torch.float32, (T, None))
+    _need(weight, "weight", torch.float32)
+    if g_off < 0 or g_off + W > gate.shape[1] or W % part or W % weight.numel():
+        raise KernelError("gate columns, group size or weight length do not fit the rows")
+    _ok(kernels_lib().xb_gated_head_norm(dtype_code(out.dtype), out.data_ptr(), y.data_ptr(), gate.data_ptr(), gate.shape[1],
+                                         int(g_off), weight.data_ptr(), weight.numel(), T, W, int(part), float(eps),
+                                         int(bool(gate_after)), _stream()), "gated_head_norm")

@@ -22,16 +22,25 @@ from ..weights.loader import WeightSpec, WeightStore
 def model_weight_specs(plan: ModelPlan) -> List[WeightSpec]:
     """Every tensor the model needs, in file order."""
     specs = [WeightSpec(plan.embed_name, (plan.vocab_size, plan.hidden), "embedding")]
+    if plan.pair_embedding is not None:
+        specs.append(WeightSpec(plan.pair_embedding.name, (plan.pair_embedding.buckets + 1, plan.hidden), "embedding"))
+    if plan.position_table is not None:
+        specs.append(WeightSpec(plan.position_table, (plan.max_positions, plan.hidden), "embedding"))
     for b in plan.blocks:
         specs += Block.weight_specs(b)
     specs += part_class("norm", plan.final_norm.kind).weight_specs(plan.final_norm, plan.final_norm_name)
     if plan.head_name is not None:
         specs.append(WeightSpec(plan.head_name, (plan.vocab_size, plan.hidden), "linear"))
-    names = [s.name for s in specs]
-    if len(set(names)) != len(names):
-        dup = sorted({n for n in names if names.count(n) > 1})
-        raise ValueError("the plan declares tensors twice: " + ", ".join(dup))
-    return specs
+    # a tensor that several parts read (a table shared by all layers) is declared by each of them, alike
+    seen: Dict[str, WeightSpec] = {}
+    out: List[WeightSpec] = []
+    for s in specs:
+        if s.name not in seen:
+            seen[s.name] = s
+            out.append(s)
+        elif seen[s.name] != s:
+            raise ValueError(f"the plan declares the tensor '{s.name}' twice, with different shapes or kinds")
+    return out
 
 
 class DecoderModel:
@@ -46,11 +55,18 @@ class DecoderModel:
         self.stream_dtype = torch.float32 if plan.residual_dtype == "float32" else dtype
         self.embed = None
         self.head = None
+        self.pair_table = self.pos_table = None
+        # the model's own per-request state (``state_need_of_model``), bound by the runner
+        self.model_state: Dict[str, torch.Tensor] = {}
 
     # ---- weights -------------------------------------------------------------------------------
     def load(self, store: WeightStore) -> None:
         store.check(model_weight_specs(self.plan))
         self.embed = store.get(self.plan.embed_name, self.device, self.dtype, operand=True)
+        if self.plan.pair_embedding is not None:
+            self.pair_table = store.get(self.plan.pair_embedding.name, self.device, self.dtype, operand=True)
+        if self.plan.position_table is not None:
+            self.pos_table = store.get(self.plan.position_table, self.device, self.dtype, operand=True)
         for b in self.blocks:
             b.load(store)
         self.final_norm.load(store)
@@ -68,8 +84,16 @@ class DecoderModel:
         visit(self)
         visit(self.final_norm)
         for b in self.blocks:
+            for t in b.gains.values():
+                if t.data_ptr() not in seen:
+                    seen.add(t.data_ptr())
+                    total += t.numel() * t.element_size()
             for part in b.all_parts():
                 visit(part)
+                if getattr(getattr(part, "spec", None), "out_norms", None) is not None:
+                    # two mixers side by side that keep their output projections apart hold their own weights
+                    visit(part.left)
+                    visit(part.right)
         return total
 
     def graph_safe(self) -> bool:
@@ -84,6 +108,15 @@ class DecoderModel:
             mixer = self.blocks[run.block].mixer
             out.append(mixer.cache_need() if mixer is not None else None)
         return out
+
+    def state_need_of_model(self):
+        """Per-request state that belongs to no layer: the token before, for the pair embedding."""
+        if self.plan.pair_embedding is not None:
+            return {"prev_token": ((), torch.int32)}
+        return None
+
+    def bind_state(self, tables: Dict[str, torch.Tensor]) -> None:
+        self.model_state = dict(tables)
 
     def state_needs(self):
         mixers = [self.blocks[run.block].mixer for run in self.plan.runs]
@@ -106,7 +139,19 @@ class DecoderModel:
         trace = tracing.ENABLED
         if trace:
             tracing.push("embedding")
-        kernels.embedding(x, self.embed, ctx.token_ids, ctx.err, ctx.sampled, scale=self.plan.embed_scale)
+        if self.pair_table is not None or self.pos_table is not None:
+            pair = self.plan.pair_embedding
+            prev = self.model_state.get("prev_token")
+            if pair is not None and prev is None:
+                raise RuntimeError("the pair embedding needs the model's per-request state (bind_state)")
+            kernels.embed_sum(x, self.embed, ctx.token_ids, ctx.err, sampled=ctx.sampled, scale=self.plan.embed_scale,
+                              pair=self.pair_table, pair_rule=(pair.buckets, pair.mul_prev, pair.mul_cur) if pair else None,
+                              pos_table=self.pos_table, positions=ctx.positions, req_of_token=ctx.req_of_token,
+                              q_start=ctx.q_start, slots=ctx.slots, prev_state=prev)
+            if pair is not None:
+                kernels.prev_store(prev, ctx.token_ids, ctx.sampled, ctx.q_start, ctx.slots, ctx.num_entries)
+        else:
+            kernels.embedding(x, self.embed, ctx.token_ids, ctx.err, ctx.sampled, scale=self.plan.embed_scale)
         if trace:
             tracing.pop()
         stream = Stream(x)

@@ -117,7 +117,19 @@ def _declare_kernels(lib):
     _sig(lib, "xb_embedding_f32", I, [I, P, P, P, P, I, I, I, I, F, P, P])
     _sig(lib, "xb_rmsnorm_f32", I, [I, I, P, P, P, P, P, P, I, I, I, F, F, P, P])
     _sig(lib, "xb_add_f32", I, [I, P, P, P, L, F, P])
-    _sig(lib, "xb_qkv_prepare", I, [I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, F, P, P])
+    _sig(lib, "xb_qkv_prepare", I, [I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, F, P, F, I, L, P, P])
+    _sig(lib, "xb_rms_chain", I, [I, I, P, P, P, P, P, P, P, P, I, I, I, F, F, F, F, F, P, P])
+    _sig(lib, "xb_dual_rms_sum", I, [I, P, P, P, P, P, I, I, F, F, F, F, P])
+    _sig(lib, "xb_add_bias", I, [I, P, P, I, I, P])
+    _sig(lib, "xb_swiglu_bias", I, [I, I, P, P, P, I, I, I, P])
+    _sig(lib, "xb_embed_sum", I, [I, P, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, L, L, I, F, P, P])
+    _sig(lib, "xb_prev_store", I, [P, P, P, I, P, P, I, P])
+    _sig(lib, "xb_token_gate", I, [I, P, P, P, I, I, P, P, I, P, I, I, I, P, P])
+    _sig(lib, "xb_conv_silu", I, [I, P, P, L, I, P, P, P, P, P, P, I, I, I, P])
+    _sig(lib, "xb_conv_state", I, [P, P, L, I, P, P, I, I, I, P])
+    _sig(lib, "xb_selective_scan", I, [P, P, I, P, L, I, P, P, P, P, P, P, I, I, I, I, I, P])
+    _sig(lib, "xb_delta_rule", I, [P, P, I, P, L, I, P, L, P, P, P, P, P, I, I, I, I, I, F, P])
+    _sig(lib, "xb_gated_head_norm", I, [I, P, P, P, L, I, P, I, I, I, I, F, I, P])
     _sig(lib, "xb_dyt_norm", I, [I, I, I, P, P, P, P, P, P, P, P, F, P, P, P, I, I, I, P, P])
     _sig(lib, "xb_latent_prepare", I, [I, P, P, P, L, I, I, P, L, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, P, P])
     _sig(lib, "xb_attn_latent_mma_takes", I, [I, I])

@@ -23,20 +23,33 @@ from .. import kernels, tracing
 from ..config.plan import BlockSpec
 from ..weights.loader import WeightSpec
 from .base import LayerCache, Part, StepContext, build_part, part_class
+from .norm import RMSNorm, chain as norm_chain
 
 _FAMILY = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
 
 
+def _width_of(spec: BlockSpec) -> int:
+    """The width of the residual stream, from the block's first norm or part that names it."""
+    for o in spec.program:
+        if o.spec is not None:
+            w = getattr(o.spec, "dim", 0) if o.op == "norm" else getattr(o.spec, "hidden", 0)
+            if w:
+                return int(w)
+    raise ValueError(f"block '{spec.prefix}': no part names the width of the residual stream")
+
+
 class Addend:
-    """A value that waits to be added into another: ``scale * norm(t)``, where ``norm`` (a norm part, or None) has
-    not been carried out yet - the kernel that forms the sum may do it, if its kind offers that."""
+    """A value that waits to be added into another: ``scale * gain * norm(t)``, where ``norm`` (a norm part, or None)
+    has not been carried out yet - the kernel that forms the sum may do it, if its kind offers that - and ``gain`` is
+    a learned vector over the channels (or None)."""
 
-    __slots__ = ("t", "scale", "norm")
+    __slots__ = ("t", "scale", "norm", "gain")
 
-    def __init__(self, t: torch.Tensor, scale: float = 1.0, norm=None):
+    def __init__(self, t: torch.Tensor, scale: float = 1.0, norm=None, gain=None):
         self.t = t
         self.scale = scale
         self.norm = norm
+        self.gain = gain
 
     def plain(self, ctx) -> torch.Tensor:
         """The tensor with its norm carried out (in place: the unnormed value is read by nobody else)."""
@@ -47,6 +60,14 @@ class Addend:
 
 
 def _add_into(dst: torch.Tensor, a: Addend, ctx) -> None:
+    if a.gain is not None or (a.norm is not None and isinstance(a.norm, RMSNorm) and dst.dtype == torch.float32):
+        # one pass: the branch's own RMS norm, the gain, the scale and the sum
+        norm, a.norm = a.norm, None
+        if norm is not None and not RMSNorm.accepts_branch_norm(norm):
+            norm.forward(a.t, a.t, ctx)
+            norm = None
+        norm_chain(None, dst, ctx, None, a.t, a.scale, norm, a.gain, dst, None)
+        return
     kernels.add(dst, dst, a.plain(ctx), a.scale)
 
 
@@ -57,10 +78,17 @@ def fused_norm(part, out, src, ctx, last: Optional[Addend], rows=None):
         return part.forward(out, src, ctx, rows=rows) if rows is not None else part.forward(out, src, ctx)
     kw = {}
     if last.norm is not None:
-        if getattr(part, "takes_branch_norm", False) and type(last.norm) is type(part):
+        accepts = getattr(part, "accepts_branch_norm", None)
+        if getattr(part, "takes_branch_norm", False) and (accepts(last.norm) if accepts else type(last.norm) is type(part)):
             kw["branch_norm"] = last.norm
         else:
             last.plain(ctx)
+    if last.gain is not None:
+        if getattr(part, "takes_branch_gain", False):
+            kw["branch_gain"] = last.gain
+        else:
+            _add_into(src, last, ctx)
+            return part.forward(out, src, ctx, rows=rows) if rows is not None else part.forward(out, src, ctx)
     if last.scale != 1.0:
         if getattr(part, "takes_branch_scale", False):
             kw["branch_scale"] = last.scale
@@ -106,6 +134,8 @@ class Block:
                 self.parts[key] = build_part(_FAMILY[o.op], o.spec, spec.prefix + o.name, dtype, device)
         mixers = [p for (op, _), p in self.parts.items() if op == "mixer"]
         self.mixer = mixers[0] if mixers else None
+        self.device = device
+        self.gains: Dict[str, torch.Tensor] = {}      # learned vectors of the additions, by tensor name after the prefix
 
     @staticmethod
     def weight_specs(spec: BlockSpec) -> List[WeightSpec]:
@@ -116,6 +146,8 @@ class Block:
                 continue
             seen.add((o.op, o.name))
             out += part_class(_FAMILY[o.op], o.spec.kind).weight_specs(o.spec, spec.prefix + o.name)
+        for name in sorted({o.gain for o in spec.program if o.op == "add" and o.gain is not None}):
+            out.append(WeightSpec(spec.prefix + name, (_width_of(spec),), "norm"))
         return out
 
     def all_parts(self) -> List[Part]:
@@ -124,6 +156,9 @@ class Block:
     def load(self, store) -> None:
         for part in self.parts.values():
             part.load(store)
+        for o in self.spec.program:
+            if o.op == "add" and o.gain is not None and o.gain not in self.gains:
+                self.gains[o.gain] = store.get(self.spec.prefix + o.gain, self.device, torch.float32).float().contiguous()
 
     def forward(self, stream: Stream, ctx: StepContext, cache: Optional[LayerCache], state, writes_cache: bool) -> Stream:
         """Runs the program on the residual stream; returns the stream with the additions that
@@ -151,10 +186,11 @@ class Block:
         program = self.spec.program
         for idx, o in enumerate(program):
             if o.op == "add":
+                gain = self.gains[o.gain] if o.gain is not None else None
                 if o.src in lazy and not waiting.get(o.src):
-                    waiting.setdefault(o.dst, []).append(Addend(vals[o.src], o.scale, lazy.pop(o.src)))
+                    waiting.setdefault(o.dst, []).append(Addend(vals[o.src], o.scale, lazy.pop(o.src), gain))
                 else:
-                    waiting.setdefault(o.dst, []).append(Addend(read(o.src), o.scale))
+                    waiting.setdefault(o.dst, []).append(Addend(read(o.src), o.scale, None, gain))
                 continue
             part = self.parts[(o.op, o.name)]
             if o.op == "norm":

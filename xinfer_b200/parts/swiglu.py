@@ -27,17 +27,22 @@ class SwiGLU(FeedForward):
         if spec.activation not in kernels.ACTIVATIONS:
             raise ValueError(f"the gated feed-forward supports {', '.join(sorted(kernels.ACTIVATIONS))}, not '{spec.activation}'")
         self.names = tuple(spec.names) if spec.names else _DEFAULT_NAMES
-        self.w_gate_up = self.w_down = None
+        self.w_gate_up = self.w_down = self.b_gate_up = self.b_down = None
 
     @classmethod
     def weight_specs(cls, spec: FeedForwardSpec, prefix: str) -> List[WeightSpec]:
         p = prefix
         n = tuple(spec.names) if spec.names else _DEFAULT_NAMES
-        return [
+        out = [
             WeightSpec(p + n[0], (spec.intermediate, spec.hidden)),
             WeightSpec(p + n[1], (spec.intermediate, spec.hidden)),
             WeightSpec(p + n[2], (spec.hidden, spec.intermediate)),
         ]
+        if spec.bias_suffix:
+            out += [WeightSpec(p + n[0] + spec.bias_suffix, (spec.intermediate,), "around_zero"),
+                    WeightSpec(p + n[1] + spec.bias_suffix, (spec.intermediate,), "around_zero"),
+                    WeightSpec(p + n[2] + spec.bias_suffix, (spec.hidden,), "around_zero")]
+        return out
 
     def load(self, store) -> None:
         p = self.prefix
@@ -46,13 +51,23 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         del g, u
         self.w_down = store.get(p + self.names[2], self.device, self.dtype, operand=True)
+        sfx = self.spec.bias_suffix
+        if sfx:
+            self.b_gate_up = torch.cat([store.get(p + self.names[i] + sfx, self.device, torch.float32).float()
+                                        for i in range(2)]).contiguous()
+            self.b_down = store.get(p + self.names[2] + sfx, self.device, torch.float32).float().contiguous()
 
     def forward(self, x, ctx: StepContext):
         s = self.spec
         T = x.shape[0]
         ws = ctx.workspace
         act = ws.get("ffn.act", (T, s.intermediate), self.dtype)
-        if s.activation != "silu" or not gemm_backend.try_fused_gate(act, x, self.w_gate_up, ctx.err):
+        if self.b_gate_up is not None:
+            # biases: the packed product leaves float32, the gate kernel adds them before the activation
+            gu = ws.get("ffn.gate_up32", (T, 2 * s.intermediate), torch.float32)
+            linear(gu, x, self.w_gate_up, ctx.err)
+            kernels.swiglu_bias(act, gu, self.b_gate_up, s.activation)
+        elif s.activation != "silu" or not gemm_backend.try_fused_gate(act, x, self.w_gate_up, ctx.err):
             gu = ws.get("ffn.gate_up", (T, 2 * s.intermediate), self.dtype)
             linear(gu, x, self.w_gate_up, ctx.err)
             kernels.swiglu(act, gu, s.activation)
@@ -60,6 +75,8 @@ class SwiGLU(FeedForward):
         # where the stream is float32)
         out = ws.get("ffn.out", (T, s.hidden), ctx.branch_dtype or self.dtype)
         linear(out, act, self.w_down, ctx.err)
+        if self.b_down is not None:
+            kernels.add_bias(out, self.b_down)
         return out
 
 

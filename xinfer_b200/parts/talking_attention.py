@@ -24,6 +24,7 @@ from .base import CacheTensor, LayerCache, Mixer, PagedCacheNeed, StepContext, b
 from .linear import linear
 
 _DEFAULT_NAMES = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "talk.weight")
+_DEFAULT_NORM_NAMES = ("q_norm.weight", "k_norm.weight")
 # a single-token step cuts every token's keys into ranges so that about this many blocks run: one per SM (the
 # kernel's shared memory allows one block per SM; 8 requests at context 4,096 take 71.7 us in one wave of 144
 # blocks and 80.2 us in 256 blocks)
@@ -47,7 +48,7 @@ class TalkingAttention(Mixer):
         if self.position is not None and not hasattr(self.position, "frequencies"):
             raise ValueError("this attention needs a rotary position encoding that offers its frequencies")
         self.names = tuple(spec.names) if spec.names else _DEFAULT_NAMES
-        self.w_qkv = self.w_o = self.talk = self.q_norm = self.k_norm = None
+        self.w_qkv = self.w_o = self.talk = self.q_norm = self.k_norm = self.bias = None
 
     @classmethod
     def weight_specs(cls, spec: AttentionSpec, prefix: str) -> List[WeightSpec]:
@@ -62,20 +63,33 @@ class TalkingAttention(Mixer):
         if spec.talking_heads:
             out.append(WeightSpec(prefix + n[4], (spec.num_heads, spec.num_heads), "unit"))
         if spec.qk_norm and spec.qk_norm_weight:
-            out += [WeightSpec(prefix + "q_norm.weight", (d,), "norm"), WeightSpec(prefix + "k_norm.weight", (d,), "norm")]
+            qn, kn = spec.qk_norm_names or _DEFAULT_NORM_NAMES
+            out += [WeightSpec(prefix + qn, (d,), "norm"), WeightSpec(prefix + kn, (d,), "norm")]
+        if spec.bias_suffix:
+            out += [WeightSpec(prefix + n[0] + spec.bias_suffix, (spec.num_heads * d,), "around_zero"),
+                    WeightSpec(prefix + n[1] + spec.bias_suffix, (spec.num_kv_heads * d,), "around_zero"),
+                    WeightSpec(prefix + n[2] + spec.bias_suffix, (spec.num_kv_heads * dv,), "around_zero")]
+        if spec.gate_name:
+            out.append(WeightSpec(prefix + spec.gate_name, (spec.num_heads * dv, spec.hidden)))
         return out
 
     def load(self, store) -> None:
         p, n, s = self.prefix, self.names, self.spec
         parts = [store.get(p + n[i], self.device, self.dtype, operand=True) for i in range(3)]
+        if s.gate_name:     # the gate reads the same input: one product gives [q | k | v | gate]
+            parts.append(store.get(p + s.gate_name, self.device, self.dtype, operand=True))
         self.w_qkv = torch.cat(parts, dim=0).contiguous()
         del parts
+        if s.bias_suffix:
+            self.bias = torch.cat([store.get(p + n[i] + s.bias_suffix, self.device, torch.float32).float()
+                                   for i in range(3)]).contiguous()
         self.w_o = store.get(p + n[3], self.device, self.dtype, operand=True)
         if s.talking_heads:
             self.talk = store.get(p + n[4], self.device, torch.float32).float().contiguous()
         if s.qk_norm and s.qk_norm_weight:
-            self.q_norm = store.get(p + "q_norm.weight", self.device, torch.float32).float().contiguous()
-            self.k_norm = store.get(p + "k_norm.weight", self.device, torch.float32).float().contiguous()
+            qn, kn = s.qk_norm_names or _DEFAULT_NORM_NAMES
+            self.q_norm = store.get(p + qn, self.device, torch.float32).float().contiguous()
+            self.k_norm = store.get(p + kn, self.device, torch.float32).float().contiguous()
 
     def cache_need(self) -> PagedCacheNeed:
         s = self.spec
@@ -108,8 +122,14 @@ class TalkingAttention(Mixer):
         T = x.shape[0]
         nh, nkv, d, dv = s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim
         ws = ctx.workspace
-        qkv = ws.get("tattn.qkv", (T, (nh + nkv) * d + nkv * dv), self.dtype)
-        linear(qkv, x, self.w_qkv, ctx.err)
+        nqkv = (nh + nkv) * d + nkv * dv
+        if s.gate_name:
+            proj = ws.get("tattn.qkvg", (T, nqkv + nh * dv), self.dtype)
+            linear(proj, x, self.w_qkv, ctx.err)
+            qkv = proj
+        else:
+            qkv = ws.get("tattn.qkv", (T, nqkv), self.dtype)
+            linear(qkv, x, self.w_qkv, ctx.err)
         q = ws.get("tattn.q", (T, nh, d), self.dtype)
         table, stride = ctx.tables[cache.group], ctx.strides[cache.group]
         rope = self.position.spec if self.position is not None else None
@@ -118,7 +138,17 @@ class TalkingAttention(Mixer):
                             self.position.frequencies() if rope is not None else None, ctx.positions, ctx.req_of_token,
                             table, stride, nh, nkv, d, dv, rope.rotary_dim if rope is not None else 0,
                             rope is not None and rope.layout == "interleaved", norm_mode, s.qk_norm_eps, writes_cache,
-                            ctx.err, rot_magnitude=rope.magnitude if rope is not None else 1.0)
+                            ctx.err, rot_magnitude=rope.magnitude if rope is not None else 1.0, bias=self.bias,
+                            q_temp=s.q_temp, row_len=qkv.shape[1])
+        self._attend(q, ctx, cache, table, stride, out, out_scale)
+        if s.gate_name:
+            kernels.gate_sigmoid(out, out.view(T, nh, dv).transpose(0, 1), qkv[:, nqkv:])
+
+    def _attend(self, q, ctx: StepContext, cache: LayerCache, table, stride, out, out_scale) -> None:
+        s = self.spec
+        T = q.shape[0]
+        nh, nkv, d, dv = s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim
+        ws = ctx.workspace
         if self._plain_softmax() and out_scale == 1.0 and out.is_contiguous():
             from . import attention_backend
             attention_backend.attend(out.view(T, nh, dv), q, cache, ctx, table, stride, s.window, s.scale)

@@ -65,6 +65,15 @@ class WeightSpec:
     init: str = "linear"
     param: int = 0
 
+    # A dimension of -1 is whatever the file holds (a size that no configuration key names, such as the inner size of
+    # a low-rank map); the random-weights mode gives such a dimension ``param`` entries.
+    def concrete_shape(self) -> Tuple[int, ...]:
+        return tuple(int(self.param) if d < 0 else int(d) for d in self.shape)
+
+
+def shape_fits(have: Sequence[int], want: Sequence[int]) -> bool:
+    return len(have) == len(want) and all(w < 0 or int(h) == int(w) for h, w in zip(have, want))
+
 
 _FLOATS = (torch.float16, torch.bfloat16, torch.float32, torch.float64)
 _INTS = (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8)
@@ -98,7 +107,7 @@ class WeightStore:
             if f is None:
                 continue
             e = f.entries[n]
-            if tuple(e.shape) != shape:
+            if not shape_fits(tuple(e.shape), shape):
                 wrong_shape.append((n, e.shape, shape))
             if e.dtype not in _FLOATS and e.dtype not in _INTS:
                 wrong_dtype.append((n, str(e.dtype)))
@@ -111,14 +120,21 @@ class WeightStore:
                           f"loaded: {shown}", UnexpectedWeightsWarning, stacklevel=2)
         return unexpected
 
+    def shape(self, name: str) -> Tuple[int, ...]:
+        """The stored shape of a tensor (for sizes that only the file knows)."""
+        return tuple(self.index[name].entries[name].shape)
+
     def raw(self, name: str) -> torch.Tensor:
         """The stored tensor on the CPU, in its stored dtype."""
         return self.index[name].tensor(name)
 
-    def get(self, name: str, device, compute_dtype: torch.dtype, *, operand: bool = False) -> torch.Tensor:
+    def get(self, name: str, device, compute_dtype: torch.dtype, *, operand: bool = False, columns=None) -> torch.Tensor:
         """``operand``: the tensor is an operand of the engine's matrix products and takes
-        ``compute_dtype`` whatever it was stored in (src/models/layers/linear.rs:133-138)."""
+        ``compute_dtype`` whatever it was stored in (src/models/layers/linear.rs:133-138).
+        ``columns`` = (first, end): only these columns of a matrix (cut before it crosses to the device)."""
         t = self.raw(name)
+        if columns is not None:
+            t = t[:, int(columns[0]):int(columns[1])]
         if t.dtype in _INTS:
             return t.to(device=device, dtype=torch.int32)
         if compute_dtype == torch.float32 or (not operand and t.dtype in (torch.float32, torch.float64)):

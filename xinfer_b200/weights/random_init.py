@@ -30,7 +30,7 @@ def draw(spec: WeightSpec, seed: int, std: float, norm_std: float, dtype: torch.
     CPU and tensors drawn on the GPU with the same seed are different models."""
     g = torch.Generator(device=device)
     g.manual_seed(_seed_of(seed, spec.name))
-    shape = tuple(spec.shape)
+    shape = spec.concrete_shape() if spec.init != "choice" else tuple(spec.shape)
     if spec.init in ("linear", "embedding"):
         t = torch.randn(shape, generator=g, dtype=torch.float32, device=device).mul_(std)
     elif spec.init == "norm":
@@ -84,7 +84,7 @@ def write_random_model(model_dir: str, config_dict: Mapping[str, Any], seed: int
         return t
 
     write_safetensors(os.path.join(model_dir, "model.safetensors"),
-                      [(s.name, tuple(s.shape), stored(s)) for s in specs], produce,
+                      [(s.name, s.concrete_shape() if s.init != "choice" else tuple(s.shape), stored(s)) for s in specs], produce,
                       metadata={"format": "pt", "seed": str(int(seed))})
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(dict(config_dict), f, indent=1)
@@ -110,16 +110,24 @@ class RandomWeightStore:
         missing = sorted(n for n in want if n not in self.specs)
         unexpected = sorted(n for n in self.specs if n not in want)
         wrong = [(n, self.specs[n].shape, want[n]) for n in sorted(want) if n in self.specs and tuple(self.specs[n].shape) != want[n]]
+        # (a dimension of -1 stands on both sides: the same spec declares and draws)
         if missing or wrong or (strict and unexpected):
             raise WeightError(missing, unexpected, wrong)
         return unexpected
 
-    def get(self, name: str, device, compute_dtype: torch.dtype, *, operand: bool = False) -> torch.Tensor:
+    def shape(self, name: str):
+        s = self.specs[name]
+        return s.concrete_shape() if s.init != "choice" else tuple(s.shape)
+
+    def get(self, name: str, device, compute_dtype: torch.dtype, *, operand: bool = False, columns=None) -> torch.Tensor:
         spec = self.specs[name]
         target = torch.float32 if compute_dtype == torch.float32 else torch.bfloat16
         dev = torch.device(device)
         gen_dev = dev if dev.type == "cuda" else "cpu"
-        return draw(spec, self.seed, self.std, self.norm_std, target, device=gen_dev).to(dev).contiguous()
+        t = draw(spec, self.seed, self.std, self.norm_std, target, device=gen_dev)
+        if columns is not None:
+            t = t[:, int(columns[0]):int(columns[1])]
+        return t.to(dev).contiguous()
 
     def close(self) -> None:
         pass
