@@ -256,3 +256,13 @@ def load_folder(path: str, dtype=torch.float64):
         t = torch.frombuffer(bytearray(data[lo:hi]), dtype=_DT[e["dtype"]]).view(*e["shape"])
         w[name] = t.to(dtype) if t.is_floating_point() else t
     return cfg, w
+
+
+def generate(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+    """Greedy continuation by n tokens, the whole sequence recomputed for every token."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        tok = int(forward(cfg, w, seq)[-1].argmax())
+        seq.append(tok)
+        out.append(tok)
+    return out
