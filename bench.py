@@ -8,6 +8,7 @@
     python bench.py --ablate                                # a decode step with one kind of kernel left out at a time
     python bench.py --compare tidarax [--size 1k|4k]        # the Tidarax design beside Qwen3 at equal layer sizes
     python bench.py --compare dufitar [--size 1k|4k]        # the Dufitar design beside Qwen3 at equal layer sizes
+    python bench.py --compare gulipel [--size 1k|4k]        # the Gulipel design beside Tidarax at equal layer sizes
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and the context length
 of the configuration (a "step" is one decode step of the whole batch), timed on the device with
@@ -252,6 +253,31 @@ def dufitar_config(z: dict, lat: dict, layers: int, vocab: int) -> dict:
                 embedding=dict(scale=2.0), layers=out)
 
 
+# The recurrent layers of --compare gulipel: a state-space mixer twice as wide as the model in heads of 64 channels
+# with a state of 128 per channel, and a gated delta rule with as many heads as the attention beside it.
+def gulipel_sizes(z: dict) -> dict:
+    ss_heads = 2 * z["hidden"] // 64
+    return dict(ss_heads=ss_heads, ss_head_dim=64, ss_state=128, ss_groups=max(1, ss_heads // 16), conv=4,
+                delta_heads=z["heads"], delta_kv_heads=z["heads"], delta_dim=z["head_dim"], delta_vdim=z["head_dim"], rank=64)
+
+
+def gulipel_config(z: dict, layers: int, vocab: int, max_positions: int) -> dict:
+    g, d = gulipel_sizes(z), z["head_dim"]
+    dense = dict(kind="dense", ff=z["intermediate"])
+    ssm = dict(heads=g["ss_heads"], vdim=g["ss_head_dim"], state=g["ss_state"], groups=g["ss_groups"], conv=g["conv"],
+               norm_groups=g["ss_groups"])
+    par = dict(left=dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, q_temp=dict(coef=0.3, every=256)),
+               right=dict(heads=g["delta_heads"], kv_heads=g["delta_kv_heads"], dim=g["delta_dim"], vdim=g["delta_vdim"], conv=g["conv"],
+                          decay_rank=g["rank"], gate_rank=g["rank"]))
+    # state-space layers with a parallel layer every other one: as many attention layers per model as a Tidarax
+    # model of half the depth, the rest recurrent
+    out = [dict(type="parallel", mixer=par, mlp=dense) if i % 2 == 1 else dict(type="mamba2" if i % 4 == 0 else "mamba2_2", mixer=ssm, mlp=dense)
+           for i in range(layers)]
+    return dict(architecture="Gulipel", vocab=vocab, width=z["hidden"], norm=dict(eps=1e-5), max_positions=max_positions,
+                logit_softcap=30.0, embedding=dict(scale=z["hidden"] ** 0.5, bigram=dict(buckets=100003, mul_prev=127, mul_cur=17)),
+                token_side=dict(dim=64), layers=out)
+
+
 def compare(args) -> int:
     """Prefill and decode throughput of a model of the named design and of a Qwen3 model of the same layer sizes
     (random weights, `--layers` layers each, default 4), then the design's kernels one by one beside their like
@@ -263,12 +289,14 @@ def compare(args) -> int:
     pk = peaks()
     z = COMPARE_SIZES[args.size]
     L, V, B, ctx_len = args.layers or 4, 32000, args.batch, 2048
-    models = {
-        ("Tidarax" if args.compare == "tidarax" else "Dufitar"):
-            tidarax_config(z, L, V) if args.compare == "tidarax" else dufitar_config(z, LATENT_SIZES[args.size], L, V),
-        "Qwen3": dict(CONFIG, vocab_size=V, hidden_size=z["hidden"], intermediate_size=z["intermediate"], num_hidden_layers=L,
-                      num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"]),
-    }
+    qwen3 = dict(CONFIG, vocab_size=V, hidden_size=z["hidden"], intermediate_size=z["intermediate"], num_hidden_layers=L,
+                 num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"])
+    if args.compare == "gulipel":       # its closest model is the other one with two mixers side by side
+        models = {"Gulipel": gulipel_config(z, L, V, ctx_len + 128), "Tidarax": tidarax_config(z, L, V)}
+    elif args.compare == "tidarax":
+        models = {"Tidarax": tidarax_config(z, L, V), "Qwen3": qwen3}
+    else:
+        models = {"Dufitar": dufitar_config(z, LATENT_SIZES[args.size], L, V), "Qwen3": qwen3}
     rng = np.random.default_rng(0)
     for name, cfg in models.items():
         pages = (ctx_len + 64 + PAGE - 1) // PAGE + 1
@@ -314,7 +342,10 @@ def compare(args) -> int:
                           "dtype": "bf16", "data": "synthetic (random weights, seeded uniform token ids)"}), flush=True)
         del runner
         torch.cuda.empty_cache()
-    if args.compare == "dufitar":
+    if args.compare == "gulipel":
+        records = measure.gulipel_kernels(hidden=z["hidden"], heads=z["heads"], kv_heads=z["kv_heads"], head_dim=z["head_dim"],
+                                          intermediate=z["intermediate"], hbm_gbs=pk["hbm_gbs"], **gulipel_sizes(z))
+    elif args.compare == "dufitar":
         lat = LATENT_SIZES[args.size]
         records = measure.dufitar_kernels(hidden=z["hidden"], heads=z["heads"], kv_heads=z["kv_heads"], head_dim=z["head_dim"],
                                           intermediate=z["intermediate"], kv_rank=lat["kv_rank"], rot_dim=lat["rot_dim"],
@@ -352,9 +383,9 @@ def main() -> int:
                     help="with --kernels: the attention kernels alone at this head layout, over short and long contexts")
     ap.add_argument("--case", default="", metavar="decode:BATCHxCONTEXT | prefill:CACHED+NEW",
                     help="with --kernels --attn: this one case instead of the standard ones")
-    ap.add_argument("--compare", default="", choices=["", "tidarax", "dufitar"],
-                    help="instead of the step benchmark: prefill and decode throughput of this design beside Qwen3 at equal "
-                         "layer sizes, and its kernels beside their like kernels; one JSON line each")
+    ap.add_argument("--compare", default="", choices=["", "tidarax", "dufitar", "gulipel"],
+                    help="instead of the step benchmark: prefill and decode throughput of this design beside its closest model "
+                         "(Qwen3; for gulipel, Tidarax) at equal layer sizes, and its kernels beside their like kernels; one JSON line each")
     ap.add_argument("--size", default="4k", choices=sorted(COMPARE_SIZES), help="layer sizes of --compare")
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the step benchmark, time single kernels at serving sizes: one JSON line each")

@@ -585,3 +585,119 @@ def dufitar_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
     if int(err):
         raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
     return out
+
+
+def gulipel_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, head_dim: int = 128, intermediate: int = 12288,
+                    ss_heads: int = 128, ss_head_dim: int = 64, ss_state: int = 128, ss_groups: int = 8, conv: int = 4,
+                    delta_heads: int = 32, delta_kv_heads: int = 32, delta_dim: int = 128, delta_vdim: int = 128, rank: int = 64,
+                    tokens: int = 2048, decode_batch: int = 8, hbm_gbs: float = 0.0, device="cuda:0") -> List[Dict]:
+    """One record per kernel that the Gulipel path adds: time, bytes and the share of its floor (the bytes that must
+    cross memory at the measured copy rate; for the two scans over a prompt also the floor of their arithmetic at the
+    nominal FMA rate), beside the like kernels of the Tidarax path at the same width."""
+    out: List[Dict] = []
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    sets = 4
+    f32 = lambda *shape: torch.randn(*shape, device=device)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+
+    def record(name, nbytes, run, like=None, flops=0.0, n=sets, **more):
+        us = _loop_time_us(lambda: [run(i) for i in range(n)]) / n
+        rec = {"kernel": name, "bytes": nbytes, "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1)}
+        floor_us = nbytes / (hbm_gbs or 6650.0) / 1e3
+        if flops:
+            rec["fp32_tflops"] = round(flops / us / 1e6, 2)
+            floor_us = max(floor_us, flops / FP32_FMA_TFLOPS_NOMINAL / 1e6)
+        rec["floor_us"] = round(floor_us, 1)
+        rec["frac_of_floor"] = round(floor_us / us, 3)
+        if like:
+            rec["like"] = like
+        rec.update(more)
+        out.append(rec)
+
+    q_start, slots, req = i32([0, tokens]), i32([0]), torch.zeros(tokens, dtype=torch.int32, device=device)
+    B = decode_batch
+    dq_start, dslots, dreq = i32(list(range(B + 1))), i32(list(range(B))), i32(list(range(B)))
+
+    # the state-space mixer: convolution, scan, gate and norm
+    H, P, N, G = ss_heads, ss_head_dim, ss_state, ss_groups
+    inner = H * P
+    C = inner + 2 * G * N
+    for what, T, qs, sl, rq, ne in (("a prompt", tokens, q_start, slots, req, 1), ("single tokens", B, dq_start, dslots, dreq, B)):
+        projs = [f32(T, inner + C + H) for _ in range(sets)]
+        xbcs = [torch.empty(T, C, device=device) for _ in range(sets)]
+        ys = [torch.empty(T, inner, device=device) for _ in range(sets)]
+        gated = [torch.empty(T, inner, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+        taps, cb = f32(C, conv), f32(C)
+        cstates = [torch.zeros(ne, conv - 1, C, device=device) for _ in range(sets)]
+        states = [torch.zeros(ne, H, N, P, device=device) for _ in range(sets)]
+        dtb, alog, dsk, nw = f32(H), f32(H), f32(H), f32(inner)
+        state_bytes = 0 if T > B else 2 * ne * H * N * P * 4
+        record(f"short convolution + SiLU, {what}", T * C * 8, lambda i: kernels.conv_silu(
+            xbcs[i], projs[i], inner, taps, cb, cstates[i], rq, qs, sl, ne), "SiLU gate", tokens=T, channels=C)
+        record(f"state-space scan, {what}", T * (C + inner + H) * 4 + (state_bytes or 2 * H * N * P * 4), lambda i: kernels.selective_scan(
+            ys[i], xbcs[i], projs[i], inner + C, dtb, alog, dsk, states[i], qs, sl, ne, H, P, N, G),
+            "gated recurrence over a prompt (three passes)", flops=4.0 * T * H * N * P, tokens=T, heads=H, state=N, head_dim=P)
+        record(f"gate + norm in parts, {what}", T * inner * (4 + 4 + 2), lambda i: kernels.gated_head_norm(
+            gated[i], ys[i], projs[i], 0, nw, inner // G, 1e-5, gate_after=False), "residual sum + RMSNorm", tokens=T)
+        del projs, xbcs, ys, gated, cstates, states
+
+    # the gated delta rule
+    H, G, d, dv = delta_heads, delta_kv_heads, delta_dim, delta_vdim
+    Cq = 2 * G * d + H * dv
+    for what, T, qs, sl, rq, ne in (("a prompt", tokens, q_start, slots, req, 1), ("single tokens", B, dq_start, dslots, dreq, B)):
+        qkvs = [f32(T, Cq) for _ in range(sets)]
+        projs = [f32(T, Cq + H) for _ in range(sets)]
+        ags = [f32(T, H * d + H * dv) for _ in range(sets)]
+        os_ = [torch.empty(T, H * dv, device=device) for _ in range(sets)]
+        gated = [torch.empty(T, H * dv, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+        states = [torch.zeros(ne, H, d, dv, device=device) for _ in range(sets)]
+        dtb, alog, nw = f32(H * d), f32(H), f32(dv)
+        state_bytes = 2 * ne * H * d * dv * 4
+        record(f"gated delta rule, {what}", T * (Cq + H * d + H * dv + H) * 4 + state_bytes, lambda i: kernels.delta_rule(
+            os_[i], qkvs[i], projs[i], Cq, ags[i], dtb, alog, states[i], qs, sl, ne, H, G, d, dv),
+            "gated recurrence over a prompt (three passes)", flops=8.0 * T * H * d * dv, tokens=T, heads=H, dim=d, vdim=dv)
+        record(f"norm per head + gate, {what}", T * H * dv * (4 + 4 + 2), lambda i: kernels.gated_head_norm(
+            gated[i], os_[i], ags[i], H * d, nw, dv, 1e-5, gate_after=True), "residual sum + RMSNorm", tokens=T)
+        del qkvs, projs, ags, os_, gated, states
+
+    # the residual arithmetic: norm of the branch, learned scale, sum, next norm in one pass; the two sides' average
+    T = tokens
+    xs, bs = [f32(T, hidden) for _ in range(sets)], [f32(T, hidden) for _ in range(sets)]
+    os_ = [torch.empty(T, hidden, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    w, bw, g = f32(hidden), f32(hidden), f32(hidden)
+    record("normed branch * learned scale + float32 residual sum + norm", T * hidden * (4 + 4 + 4 + 2),
+           lambda i: kernels.rms_chain(os_[i], xs[i], w, 1e-5, err, branch=bs[i], branch_weight=bw, branch_eps=1e-5, gain=g,
+                                       sum_out=xs[i]), "float32 residual sum + norm", tokens=T)
+    record("like: Tidarax float32 residual sum + norm", T * hidden * (4 + 4 + 4 + 2),
+           lambda i: kernels.rmsnorm(os_[i], xs[i], w, 1e-6, err, branch=bs[i], sum_out=xs[i], weight_offset=1.0), tokens=T)
+    ds = [torch.empty(T, hidden, device=device) for _ in range(sets)]
+    record("two sides: norm each, average", T * hidden * 12, lambda i: kernels.dual_rms_sum(ds[i], xs[i], bs[i], w, bw, 1e-5, 0.5, 0.5),
+           "float32 residual sum + norm", tokens=T)
+    del xs, bs, os_, ds
+
+    # the like kernel of the scans: Tidarax's gated recurrence (a vector state per channel) over the same prompt
+    W = hidden
+    zxgs = [f32(T, 3 * W) for _ in range(sets)]
+    ys = [torch.empty(T, W, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    bz, bx = f32(W), f32(W)
+    state = torch.zeros(2, W, device=device)
+    scratch = torch.empty(3 * T * W, device=device)
+    record("like: Tidarax gated recurrence over a prompt (three passes)", T * W * (3 * 4 + 2),
+           lambda i: kernels.gated_scan(ys[i], zxgs[i], bz, bx, state, q_start, slots, req, 1, 1.0, scratch), tokens=T)
+    del zxgs, ys, scratch
+
+    # the embedding's three terms
+    V, buckets = 32000, 100003
+    table, pair, pos = (torch.randn(V, hidden, device=device).bfloat16(), torch.randn(buckets + 1, hidden, device=device).bfloat16(),
+                        torch.randn(T, hidden, device=device).bfloat16())
+    ids = torch.randint(0, V, (T,), device=device, dtype=torch.int32)
+    xs = [torch.empty(T, hidden, device=device) for _ in range(sets)]
+    prev = torch.zeros(1, dtype=torch.int32, device=device)
+    positions = torch.arange(T, dtype=torch.int32, device=device)
+    record("embedding row * scale + pair row + position row", T * hidden * (3 * 2 + 4),
+           lambda i: kernels.embed_sum(xs[i], table, ids, err, scale=4.0, pair=pair, pair_rule=(buckets, 31, 7), pos_table=pos,
+                                       positions=positions, req_of_token=req, q_start=q_start, slots=slots, prev_state=prev),
+           "embedding", tokens=T)
+    if int(err):
+        raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
+    return out
