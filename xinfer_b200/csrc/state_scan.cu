@@ -5,196 +5,434 @@
 //                                                             o = S^T q      (the read-out sees the token's own write)
 //   gated_head_norm_kernel  the gate and the RMS norm over a head (or a group of channels) behind either
 //
-// Layout of both scans: a block takes one (request, head) and a tile of the state's columns (columns never mix);
-// a column's rows are dealt out to DS neighbouring lanes, each keeping R of them in registers, and sums over
-// rows are folded with shuffles.  Tokens of a request are walked in order; the state is read from state[slot] at
-// the step's first token and left there after its last, so a cut between steps changes nothing but when the
-// state crosses memory.  Everything is float32: decays, softplus, exponentials, step sizes, unit norms, gates.
+// Layout of both scans: a block takes one (request, head) and a tile of the state's columns (columns never mix).
+// Its first warps compute: a lane keeps kRows rows of two neighbouring columns in registers; DS lanes of a warp
+// share a column pair and fold their sums over rows with shuffles.  Its last warps feed them: tokens of a request
+// are walked in order, a tile of TT tokens at a time, and while the computing warps work on one tile the feeding
+// warps bring the next one into shared memory with asynchronous copies, work out what every column needs alike
+// (step sizes, decays, unit vectors, beta) once per token, and write the tile before to memory.  The step loop
+// reads broadcast vectors from shared memory only.  One block barrier per tile hands the buffers over.  The state
+// is read from state[slot] at the step's first token and left there after its last, so a cut between steps changes
+// nothing but when the state crosses memory.  Everything is float32: decays, softplus, exponentials, step sizes,
+// unit norms, gates.
 #include "common.cuh"
 
 __device__ __forceinline__ float softplus_f32(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 __device__ __forceinline__ float sigmoid_exact(float v) { return 1.f / (1.f + expf(-v)); }
 
-template <int DS>
-__device__ __forceinline__ float fold(float v) {
-#pragma unroll
-    for (int o = DS / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
+namespace {
+constexpr int kRows = 16;            // state rows a lane keeps per column
+constexpr int kRowsPad = kRows + 4;  // the same rows in shared memory, spaced so that row groups fall on different banks
+constexpr int kScanTile = 16;        // tokens per tile, at most
+
+__device__ __forceinline__ void scan_cp4(float* dst, const float* src) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(src) : "memory");
+}
+__device__ __forceinline__ void scan_cp16(float* dst, const float* src) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(src) : "memory");
+}
+__device__ __forceinline__ void scan_cp_land() {
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncwarp();
 }
 
+// lanes of a warp are laid out [DS row groups][32 / DS column pairs]; the sum runs over the row groups
+template <int DS>
+__device__ __forceinline__ float fold_rows(float v) {
+#pragma unroll
+    for (int o = 16; o >= 32 / DS; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_total(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ int padded_row(int j) { return (j / kRows) * kRowsPad + (j % kRows); }
+
+// A row vector of `len` floats (rows up to `padded` are zero) into the padded layout; `vec` says that source and
+// length allow 16-byte copies.
+__device__ __forceinline__ void stage_rows(float* dst, const float* src, int len, int padded, int lane, bool vec) {
+    if (vec) {
+        for (int j = lane * 4; j < padded; j += 128) {
+            if (j < len)
+                scan_cp16(dst + padded_row(j), src + j);
+            else
+                *reinterpret_cast<float4*>(dst + padded_row(j)) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    } else {
+        for (int j = lane; j < padded; j += 32) {
+            if (j < len)
+                scan_cp4(dst + padded_row(j), src + j);
+            else
+                dst[padded_row(j)] = 0.f;
+        }
+    }
+}
+// The block's columns [c_base, c_base + VT) of a row of `cols` columns; the ones past the end are zero.
+__device__ __forceinline__ void stage_cols(float* dst, const float* src, int c_base, int cols, int VT, int lane, bool vec) {
+    if (vec) {
+        for (int c = lane * 4; c < VT; c += 128) {
+            if (c_base + c < cols)
+                scan_cp16(dst + c, src + c_base + c);
+            else
+                *reinterpret_cast<float4*>(dst + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    } else {
+        for (int c = lane; c < VT; c += 32) {
+            if (c_base + c < cols)
+                scan_cp4(dst + c, src + c_base + c);
+            else
+                dst[c] = 0.f;
+        }
+    }
+}
+}  // namespace
+
 // xbc[t] = [x: H*P | B: G*N | C: G*N] after the short convolution; dt is column dt_off + h of proj[t] (before
-// the bias and the softplus).  state [slots, H, N, P].  y [T, H*P].
-template <int DS, int R>
-__global__ void selective_scan_kernel(float* __restrict__ y, const float* __restrict__ xbc, int C,
-                                      const float* __restrict__ proj, long long ldp, int dt_off,
-                                      const float* __restrict__ dt_bias, const float* __restrict__ A_log,
-                                      const float* __restrict__ Dv, float* __restrict__ state,
-                                      const int* __restrict__ q_start, const int* __restrict__ slots, int H, int P, int N,
-                                      int G) {
+// the bias and the softplus).  state [slots, H, N, P].  y [T, H*P].  Shared memory: two stages of
+// B[TT][NP] C[TT][NP] x[TT][VT] dt[TT] dec[TT], then two tiles y[TT][VT].  `cw` of the block's warps compute.
+template <int DS>
+__global__ void __launch_bounds__(384, 1) selective_scan_kernel(float* __restrict__ y, const float* __restrict__ xbc, int C,
+                                                             const float* __restrict__ proj, long long ldp, int dt_off,
+                                                             const float* __restrict__ dt_bias,
+                                                             const float* __restrict__ A_log, const float* __restrict__ Dv,
+                                                             float* __restrict__ state, const int* __restrict__ q_start,
+                                                             const int* __restrict__ slots, int H, int P, int N, int G,
+                                                             int TT, int stage, int cw, int vec) {
+    extern __shared__ __align__(16) float scan_smem[];
+    constexpr int CGW = 32 / DS, NP = DS * kRowsPad, NR = DS * kRows;
     const int b = blockIdx.x, h = blockIdx.y;
-    const int VT = blockDim.x / DS;
-    const int col = threadIdx.x / DS, ds = threadIdx.x % DS;
-    const int p = blockIdx.z * VT + col;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int VT = cw * CGW * 2, c_base = blockIdx.z * VT;
     const int slot = slots[b];
     const int t0 = q_start[b], t1 = q_start[b + 1];
     if (slot < 0 || t1 <= t0) return;
-    const bool active = p < P;
     const int inner = H * P, g = h / (H / G);
-    const float A = expf(A_log[h]), dtb = dt_bias[h], Dh = Dv[h];
-    float S[R];
+    const int ntiles = (t1 - t0 + TT - 1) / TT;
+    float* sy = scan_smem + 2 * stage;
+    if (w >= cw) {
+        // feeding warps: warp `pi` of `pw` takes tokens pi, pi + pw, ... of every tile
+        const int pi = w - cw, pw = (blockDim.x >> 5) - cw;
+        const float A = expf(A_log[h]), dtb = dt_bias[h];
+        auto bring = [&](int tile) {
+            float* sB = scan_smem + (tile & 1) * stage;
+            float* sC = sB + TT * NP;
+            float* sx = sC + TT * NP;
+            float* sdt = sx + TT * VT;
+            const int tb = t0 + tile * TT, nt = min(TT, t1 - tb);
+            for (int tt = pi; tt < nt; tt += pw) {
+                const float* row = xbc + (size_t)(tb + tt) * C;
+                stage_rows(sB + tt * NP, row + inner + g * N, N, NR, lane, vec);
+                stage_rows(sC + tt * NP, row + inner + (G + g) * N, N, NR, lane, vec);
+                stage_cols(sx + tt * VT, row + h * P, c_base, P, VT, lane, vec);
+            }
+            const int mine = pi + lane * pw;
+            if (mine < nt) scan_cp4(sdt + mine, proj + (size_t)(tb + mine) * ldp + dt_off + h);
+            scan_cp_land();
+            if (mine < nt) {
+                const float dt = softplus_f32(sdt[mine] + dtb);
+                sdt[mine] = dt;
+                sdt[TT + mine] = expf(-A * dt);
+            }
+        };
+        auto leave = [&](int tile) {
+            const float* src = sy + (tile & 1) * TT * VT;
+            const int tb = t0 + tile * TT, nt = min(TT, t1 - tb);
+            for (int tt = pi; tt < nt; tt += pw)
+                for (int c = lane; c < VT; c += 32)
+                    if (c_base + c < P) y[(size_t)(tb + tt) * inner + h * P + c_base + c] = src[tt * VT + c];
+        };
+        bring(0);
+        __syncthreads();
+        for (int tile = 0; tile < ntiles; ++tile) {
+            if (tile + 1 < ntiles) bring(tile + 1);
+            if (tile > 0) leave(tile - 1);
+            __syncthreads();
+        }
+        leave(ntiles - 1);
+        return;
+    }
+    const int ds = lane / CGW, cl = (w * CGW + lane % CGW) * 2, p0 = c_base + cl;
+    const float Dh = Dv[h];
+    float S0[kRows], S1[kRows];
     float* st = state + ((size_t)slot * H + h) * N * P;
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int n = ds + r * DS;
-        S[r] = (active && n < N) ? st[(size_t)n * P + p] : 0.f;
+    for (int r = 0; r < kRows; ++r) {
+        const int n = ds * kRows + r;
+        S0[r] = (n < N && p0 < P) ? st[(size_t)n * P + p0] : 0.f;
+        S1[r] = (n < N && p0 + 1 < P) ? st[(size_t)n * P + p0 + 1] : 0.f;
     }
-    for (int t = t0; t < t1; ++t) {
-        const float dt = softplus_f32(proj[(size_t)t * ldp + dt_off + h] + dtb);
-        const float dec = expf(-A * dt);
-        const float* row = xbc + (size_t)t * C;
-        const float xv = active ? row[h * P + p] : 0.f;
-        const float* Bp = row + inner + g * N;
-        const float* Cp = Bp + G * N;
-        const float dx = dt * xv;
-        float acc = 0.f;
+    __syncthreads();
+    for (int tile = 0; tile < ntiles; ++tile) {
+        const float* sB = scan_smem + (tile & 1) * stage + ds * kRowsPad;
+        const float* sC = sB + TT * NP;
+        const float* sx = scan_smem + (tile & 1) * stage + 2 * TT * NP;
+        const float* sdt = sx + TT * VT;
+        sx += cl;
+        float* out = sy + (tile & 1) * TT * VT + cl;
+        const int nt = min(TT, t1 - t0 - tile * TT);
+        for (int tt = 0; tt < nt; ++tt, sB += NP, sC += NP, sx += VT, out += VT) {
+            const float dt = sdt[tt], dec = sdt[TT + tt];
+            const float2 xv = *reinterpret_cast<const float2*>(sx);
+            const float dx0 = dt * xv.x, dx1 = dt * xv.y;
+            const float4* Bp = reinterpret_cast<const float4*>(sB);
+            const float4* Cp = reinterpret_cast<const float4*>(sC);
+            float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int n = ds + r * DS;
-            if (n < N) {
-                S[r] = fmaf(dec, S[r], Bp[n] * dx);
-                acc = fmaf(S[r], Cp[n], acc);
+            for (int i = 0; i < kRows / 4; ++i) {
+                const float4 bv = Bp[i], cv = Cp[i];
+                const float bq[4] = {bv.x, bv.y, bv.z, bv.w}, cq[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    S0[4 * i + e] = fmaf(dec, S0[4 * i + e], bq[e] * dx0);
+                    S1[4 * i + e] = fmaf(dec, S1[4 * i + e], bq[e] * dx1);
+                    a0 = fmaf(S0[4 * i + e], cq[e], a0);
+                    a1 = fmaf(S1[4 * i + e], cq[e], a1);
+                }
             }
+            a0 = fold_rows<DS>(a0);
+            a1 = fold_rows<DS>(a1);
+            if (ds == 0) *reinterpret_cast<float2*>(out) = make_float2(fmaf(Dh, xv.x, a0), fmaf(Dh, xv.y, a1));
         }
-        acc = fold<DS>(acc);
-        if (active && ds == 0) y[(size_t)t * inner + h * P + p] = fmaf(Dh, xv, acc);
+        __syncthreads();
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int n = ds + r * DS;
-        if (active && n < N) st[(size_t)n * P + p] = S[r];
+    for (int r = 0; r < kRows; ++r) {
+        const int n = ds * kRows + r;
+        if (n < N && p0 < P) st[(size_t)n * P + p0] = S0[r];
+        if (n < N && p0 + 1 < P) st[(size_t)n * P + p0 + 1] = S1[r];
     }
 }
 
 // qkv[t] = [q: G*d | k: G*d | v: H*dv] after the short convolution; beta is column beta_off + h of proj[t] before
 // the sigmoid; ag[t] holds the decay's pre-activation for (head, key channel) at its front.  q and k become unit
 // vectors over a head (q also times d^-1/2); g = exp(-exp(A_log_h) softplus(a + dt_bias)) per (head, key channel).
-// state [slots, H, d, dv].  o [T, H*dv].
-template <int DS, int R>
-__global__ void delta_rule_kernel(float* __restrict__ o, const float* __restrict__ qkv, int Cq,
-                                  const float* __restrict__ proj, long long ldp, int beta_off,
-                                  const float* __restrict__ ag, long long ldag, const float* __restrict__ dt_bias,
-                                  const float* __restrict__ A_log, float* __restrict__ state,
-                                  const int* __restrict__ q_start, const int* __restrict__ slots, int H, int G, int d, int dv,
-                                  float unit_eps) {
+// state [slots, H, d, dv].  o [T, H*dv].  Shared memory: two stages of q[TT][DP] k[TT][DP] g[TT][DP] v[TT][VT]
+// beta[TT] kq[TT], then two tiles o[TT][VT].  With gS the decayed state, o = (gS)^T q + u (k . q).
+template <int DS>
+__global__ void __launch_bounds__(384, 1) delta_rule_kernel(float* __restrict__ o, const float* __restrict__ qkv, int Cq,
+                                                         const float* __restrict__ proj, long long ldp, int beta_off,
+                                                         const float* __restrict__ ag, long long ldag,
+                                                         const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                                                         float* __restrict__ state, const int* __restrict__ q_start,
+                                                         const int* __restrict__ slots, int H, int G, int d, int dv,
+                                                         float unit_eps, int TT, int stage, int cw, int vec) {
+    extern __shared__ __align__(16) float scan_smem[];
+    constexpr int CGW = 32 / DS, DP = DS * kRowsPad, NR = DS * kRows;
     const int b = blockIdx.x, h = blockIdx.y;
-    const int VT = blockDim.x / DS;
-    const int col = threadIdx.x / DS, ds = threadIdx.x % DS;
-    const int vc = blockIdx.z * VT + col;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int VT = cw * CGW * 2, c_base = blockIdx.z * VT;
     const int slot = slots[b];
     const int t0 = q_start[b], t1 = q_start[b + 1];
     if (slot < 0 || t1 <= t0) return;
-    const bool active = vc < dv;
     const int kvh = h / (H / G);
-    const float A = expf(A_log[h]);
-    const float qk_scale = 1.f / sqrtf((float)d);
-    float S[R], qr[R], kr[R], bias[R];
+    const int ntiles = (t1 - t0 + TT - 1) / TT;
+    float* so = scan_smem + 2 * stage;
+    if (w >= cw) {
+        // feeding warps: warp `pi` of `pw` takes tokens pi, pi + pw, ... of every tile
+        const int pi = w - cw, pw = (blockDim.x >> 5) - cw;
+        const float A = expf(A_log[h]);
+        const float qk_scale = 1.f / sqrtf((float)d);
+        const float* bias = dt_bias + (size_t)h * d;
+        auto bring = [&](int tile) {
+            float* sq = scan_smem + (tile & 1) * stage;
+            float* sk = sq + TT * DP;
+            float* sg = sk + TT * DP;
+            float* sv = sg + TT * DP;
+            float* sbeta = sv + TT * VT;
+            const int tb = t0 + tile * TT, nt = min(TT, t1 - tb);
+            for (int tt = pi; tt < nt; tt += pw) {
+                const float* row = qkv + (size_t)(tb + tt) * Cq;
+                stage_rows(sq + tt * DP, row + kvh * d, d, NR, lane, vec);
+                stage_rows(sk + tt * DP, row + (G + kvh) * d, d, NR, lane, vec);
+                stage_rows(sg + tt * DP, ag + (size_t)(tb + tt) * ldag + h * d, d, NR, lane, vec);
+                stage_cols(sv + tt * VT, row + 2 * G * d + h * dv, c_base, dv, VT, lane, vec);
+                if (lane == 0) scan_cp4(sbeta + tt, proj + (size_t)(tb + tt) * ldp + beta_off + h);
+            }
+            scan_cp_land();
+            for (int tt = pi; tt < nt; tt += pw) {
+                float* q = sq + tt * DP;
+                float* k = sk + tt * DP;
+                float* gd = sg + tt * DP;
+                float qq = 0.f, kk = 0.f;
+                for (int j = lane; j < d; j += 32) {
+                    const int at = padded_row(j);
+                    qq = fmaf(q[at], q[at], qq);
+                    kk = fmaf(k[at], k[at], kk);
+                }
+                qq = warp_total(qq);
+                kk = warp_total(kk);
+                const float qs = qk_scale / sqrtf(qq + unit_eps), ks = 1.f / sqrtf(kk + unit_eps);
+                float kq = 0.f;
+                for (int j = lane; j < d; j += 32) {
+                    const int at = padded_row(j);
+                    const float qn = q[at] * qs, kn = k[at] * ks;
+                    q[at] = qn;
+                    k[at] = kn;
+                    kq = fmaf(kn, qn, kq);
+                    gd[at] = expf(-A * softplus_f32(gd[at] + bias[j]));
+                }
+                kq = warp_total(kq);
+                if (lane == 0) {
+                    sbeta[TT + tt] = kq;
+                    sbeta[tt] = sigmoid_exact(sbeta[tt]);
+                }
+            }
+        };
+        auto leave = [&](int tile) {
+            const float* src = so + (tile & 1) * TT * VT;
+            const int tb = t0 + tile * TT, nt = min(TT, t1 - tb);
+            for (int tt = pi; tt < nt; tt += pw)
+                for (int c = lane; c < VT; c += 32)
+                    if (c_base + c < dv) o[((size_t)(tb + tt) * H + h) * dv + c_base + c] = src[tt * VT + c];
+        };
+        bring(0);
+        __syncthreads();
+        for (int tile = 0; tile < ntiles; ++tile) {
+            if (tile + 1 < ntiles) bring(tile + 1);
+            if (tile > 0) leave(tile - 1);
+            __syncthreads();
+        }
+        leave(ntiles - 1);
+        return;
+    }
+    const int ds = lane / CGW, cl = (w * CGW + lane % CGW) * 2, v0 = c_base + cl;
+    float S0[kRows], S1[kRows];
     float* st = state + ((size_t)slot * H + h) * d * dv;
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int j = ds + r * DS;
-        S[r] = (active && j < d) ? st[(size_t)j * dv + vc] : 0.f;
-        bias[r] = j < d ? dt_bias[h * d + j] : 0.f;
+    for (int r = 0; r < kRows; ++r) {
+        const int j = ds * kRows + r;
+        S0[r] = (j < d && v0 < dv) ? st[(size_t)j * dv + v0] : 0.f;
+        S1[r] = (j < d && v0 + 1 < dv) ? st[(size_t)j * dv + v0 + 1] : 0.f;
     }
-    for (int t = t0; t < t1; ++t) {
-        const float* row = qkv + (size_t)t * Cq;
-        const float* qp = row + kvh * d;
-        const float* kp = row + (G + kvh) * d;
-        const float* ap = ag + (size_t)t * ldag + h * d;
-        float sq = 0.f, sk = 0.f;
+    __syncthreads();
+    for (int tile = 0; tile < ntiles; ++tile) {
+        const float* sq = scan_smem + (tile & 1) * stage + ds * kRowsPad;
+        const float* sk = sq + TT * DP;
+        const float* sg = sk + TT * DP;
+        const float* sv = scan_smem + (tile & 1) * stage + 3 * TT * DP;
+        const float* sbeta = sv + TT * VT;
+        sv += cl;
+        float* out = so + (tile & 1) * TT * VT + cl;
+        const int nt = min(TT, t1 - t0 - tile * TT);
+        for (int tt = 0; tt < nt; ++tt, sq += DP, sk += DP, sg += DP, sv += VT, out += VT) {
+            const float beta = sbeta[tt], kq = sbeta[TT + tt];
+            const float2 vv = *reinterpret_cast<const float2*>(sv);
+            const float4* qp = reinterpret_cast<const float4*>(sq);
+            const float4* kp = reinterpret_cast<const float4*>(sk);
+            const float4* gp = reinterpret_cast<const float4*>(sg);
+            float kr[kRows];
+            float a10 = 0.f, a11 = 0.f, a20 = 0.f, a21 = 0.f;
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int j = ds + r * DS;
-            qr[r] = j < d ? qp[j] : 0.f;
-            kr[r] = j < d ? kp[j] : 0.f;
-            sq = fmaf(qr[r], qr[r], sq);
-            sk = fmaf(kr[r], kr[r], sk);
-        }
-        sq = fold<DS>(sq);
-        sk = fold<DS>(sk);
-        const float qs = qk_scale / sqrtf(sq + unit_eps), ks = 1.f / sqrtf(sk + unit_eps);
-        const float beta = sigmoid_exact(proj[(size_t)t * ldp + beta_off + h]);
-        const float vv = active ? row[2 * G * d + h * dv + vc] : 0.f;
-        float a1 = 0.f, a2 = 0.f, kq = 0.f;
+            for (int i = 0; i < kRows / 4; ++i) {
+                const float4 g4 = gp[i], k4 = kp[i], q4 = qp[i];
+                const float gq[4] = {g4.x, g4.y, g4.z, g4.w}, kq4[4] = {k4.x, k4.y, k4.z, k4.w};
+                const float qq4[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int j = ds + r * DS;
-            if (j < d) {
-                const float dec = expf(-A * softplus_f32(ap[j] + bias[r]));
-                const float kn = kr[r] * ks, qn = qr[r] * qs;
-                S[r] *= dec;
-                a1 = fmaf(S[r], kn, a1);
-                a2 = fmaf(S[r], qn, a2);
-                kq = fmaf(kn, qn, kq);
-                kr[r] = kn;
+                for (int e = 0; e < 4; ++e) {
+                    const int r = 4 * i + e;
+                    S0[r] *= gq[e];
+                    S1[r] *= gq[e];
+                    a10 = fmaf(S0[r], kq4[e], a10);
+                    a11 = fmaf(S1[r], kq4[e], a11);
+                    a20 = fmaf(S0[r], qq4[e], a20);
+                    a21 = fmaf(S1[r], qq4[e], a21);
+                    kr[r] = kq4[e];
+                }
             }
-        }
-        a1 = fold<DS>(a1);
-        a2 = fold<DS>(a2);
-        kq = fold<DS>(kq);
-        const float u = beta * (vv - a1);
+            a10 = fold_rows<DS>(a10);
+            a11 = fold_rows<DS>(a11);
+            a20 = fold_rows<DS>(a20);
+            a21 = fold_rows<DS>(a21);
+            const float u0 = beta * (vv.x - a10), u1 = beta * (vv.y - a11);
 #pragma unroll
-        for (int r = 0; r < R; ++r) S[r] = fmaf(kr[r], u, S[r]);
-        if (active && ds == 0) o[(size_t)t * H * dv + h * dv + vc] = fmaf(u, kq, a2);
+            for (int r = 0; r < kRows; ++r) {
+                S0[r] = fmaf(kr[r], u0, S0[r]);
+                S1[r] = fmaf(kr[r], u1, S1[r]);
+            }
+            if (ds == 0) *reinterpret_cast<float2*>(out) = make_float2(fmaf(u0, kq, a20), fmaf(u1, kq, a21));
+        }
+        __syncthreads();
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int j = ds + r * DS;
-        if (active && j < d) st[(size_t)j * dv + vc] = S[r];
+    for (int r = 0; r < kRows; ++r) {
+        const int j = ds * kRows + r;
+        if (j < d && v0 < dv) st[(size_t)j * dv + v0] = S0[r];
+        if (j < d && v0 + 1 < dv) st[(size_t)j * dv + v0 + 1] = S1[r];
     }
 }
 
-// rows: the smallest (DS, R) with DS * R >= rows; columns per block so that a block has up to 256 threads
-struct ScanShape {
-    int ds, r;
-};
-static inline bool scan_shape(int rows, ScanShape& s) {
-    static const ScanShape shapes[] = {{4, 4}, {4, 8}, {4, 16}, {4, 32}, {8, 32}, {16, 32}, {32, 32}};
-    for (const ScanShape& c : shapes)
-        if (c.ds * c.r >= rows) {
-            s = c;
-            return true;
-        }
-    return false;
+// Row groups per column pair: the smallest power of two with DS * kRows >= rows.
+static inline int scan_row_groups(int rows) {
+    int ds = 1;
+    while (ds * kRows < rows) ds *= 2;
+    return ds;
 }
 
-#define XB_SCAN_DISPATCH(KERNEL, ...)                                                           \
-    switch (s.ds * 100 + s.r) {                                                                \
-        case 404: KERNEL<4, 4><<<grid, threads, 0, stream>>>(__VA_ARGS__); break;              \
-        case 408: KERNEL<4, 8><<<grid, threads, 0, stream>>>(__VA_ARGS__); break;              \
-        case 416: KERNEL<4, 16><<<grid, threads, 0, stream>>>(__VA_ARGS__); break;             \
-        case 432: KERNEL<4, 32><<<grid, threads, 0, stream>>>(__VA_ARGS__); break;             \
-        case 832: KERNEL<8, 32><<<grid, threads, 0, stream>>>(__VA_ARGS__); break;             \
-        case 1632: KERNEL<16, 32><<<grid, threads, 0, stream>>>(__VA_ARGS__); break;           \
-        default: KERNEL<32, 32><<<grid, threads, 0, stream>>>(__VA_ARGS__); break;             \
+// Computing warps per block: enough to cover the columns (at most 8), fewer (down to 2) while the grid would
+// leave processors idle.
+static inline int scan_warps(int cols, int ds, long long heads_total) {
+    const int per_warp = (32 / ds) * 2;
+    int warps = 1;
+    while (warps < 8 && warps * per_warp < cols) warps *= 2;
+    while (warps > 2 && heads_total * ((cols + warps * per_warp - 1) / (warps * per_warp)) < 148) warps /= 2;
+    return warps;
+}
+
+static inline bool scan_aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+// Floats of one stage (`vectors` row vectors and two scalars per token beside the column tile), rounded so that
+// the second stage stays 16-byte aligned; the tile shrinks until two stages and two output tiles fit.
+static inline void scan_tile(int vectors, int ds, int vt, int& tt, int& stage, size_t& bytes) {
+    for (tt = kScanTile;; tt /= 2) {
+        stage = (tt * (vectors * ds * kRowsPad + vt + 2) + 3) & ~3;
+        bytes = ((size_t)2 * stage + (size_t)2 * tt * vt) * sizeof(float);
+        if (bytes <= 200 * 1024 || tt == 1) return;
     }
-
-static inline int scan_columns(int cols, int ds) {
-    // a whole number of warps; as many columns as fit 256 threads, or all of them
-    int vt = 256 / ds;
-    while (vt / 2 >= cols && vt * ds > 32) vt /= 2;
-    return vt;
 }
+
+template <typename K>
+static inline int scan_smem_opt_in(K kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return 0;
+    return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+#define XB_SCAN_DISPATCH(KERNEL, DSV, ...)                                                       \
+    switch (DSV) {                                                                              \
+        case 1: XB_SCAN_LAUNCH(KERNEL<1>, __VA_ARGS__) break;                                   \
+        case 2: XB_SCAN_LAUNCH(KERNEL<2>, __VA_ARGS__) break;                                   \
+        case 4: XB_SCAN_LAUNCH(KERNEL<4>, __VA_ARGS__) break;                                   \
+        case 8: XB_SCAN_LAUNCH(KERNEL<8>, __VA_ARGS__) break;                                   \
+        case 16: XB_SCAN_LAUNCH(KERNEL<16>, __VA_ARGS__) break;                                 \
+        default: XB_SCAN_LAUNCH(KERNEL<32>, __VA_ARGS__) break;                                 \
+    }
+#define XB_SCAN_LAUNCH(K, ...)                                  \
+    {                                                           \
+        const int rc = scan_smem_opt_in(K, bytes);              \
+        if (rc) return rc;                                      \
+        K<<<grid, threads, bytes, stream>>>(__VA_ARGS__);       \
+    }
 
 XB_EXPORT int xb_selective_scan(float* y, const float* xbc, int C, const float* proj, long long ldp, int dt_off,
                                 const float* dt_bias, const float* A_log, const float* Dv, float* state, const int* q_start,
                                 const int* slots, int entries, int H, int P, int N, int G, cudaStream_t stream) {
     if (entries <= 0) return 0;
-    ScanShape s;
-    if (!scan_shape(N, s) || H % G || entries > 2147483647 || H > 65535) return (int)cudaErrorInvalidValue;
-    const int vt = scan_columns(P, s.ds);
+    if (N < 1 || N > 32 * kRows || P < 1 || G < 1 || H % G || H > 65535) return (int)cudaErrorInvalidValue;
+    const int ds = scan_row_groups(N);
+    const int warps = scan_warps(P, ds, (long long)entries * H);
+    const int vt = warps * (32 / ds) * 2;
+    int tt, stage;
+    size_t bytes;
+    scan_tile(2, ds, vt, tt, stage, bytes);
     const dim3 grid(entries, H, (P + vt - 1) / vt);
-    const int threads = vt * s.ds;
-    XB_SCAN_DISPATCH(selective_scan_kernel, y, xbc, C, proj, ldp, dt_off, dt_bias, A_log, Dv, state, q_start, slots, H, P, N, G)
+    const int threads = (warps + 2) * 32;  // two feeding warps
+    const int vec = scan_aligned16(xbc) && C % 4 == 0 && P % 4 == 0 && N % 4 == 0 && vt % 4 == 0;
+    XB_SCAN_DISPATCH(selective_scan_kernel, ds, y, xbc, C, proj, ldp, dt_off, dt_bias, A_log, Dv, state, q_start, slots, H, P, N,
+                     G, tt, stage, warps, vec)
     return xb_launch_status();
 }
 
@@ -202,13 +440,19 @@ XB_EXPORT int xb_delta_rule(float* o, const float* qkv, int Cq, const float* pro
                             long long ldag, const float* dt_bias, const float* A_log, float* state, const int* q_start,
                             const int* slots, int entries, int H, int G, int d, int dv, float unit_eps, cudaStream_t stream) {
     if (entries <= 0) return 0;
-    ScanShape s;
-    if (!scan_shape(d, s) || H % G || H > 65535) return (int)cudaErrorInvalidValue;
-    const int vt = scan_columns(dv, s.ds);
+    if (d < 1 || d > 32 * kRows || dv < 1 || G < 1 || H % G || H > 65535) return (int)cudaErrorInvalidValue;
+    const int ds = scan_row_groups(d);
+    const int warps = scan_warps(dv, ds, (long long)entries * H);
+    const int vt = warps * (32 / ds) * 2;
+    int tt, stage;
+    size_t bytes;
+    scan_tile(3, ds, vt, tt, stage, bytes);
     const dim3 grid(entries, H, (dv + vt - 1) / vt);
-    const int threads = vt * s.ds;
-    XB_SCAN_DISPATCH(delta_rule_kernel, o, qkv, Cq, proj, ldp, beta_off, ag, ldag, dt_bias, A_log, state, q_start, slots, H, G, d,
-                     dv, unit_eps)
+    const int threads = (warps + 4) * 32;  // four feeding warps: the unit vectors and decays are theirs
+    const int vec = scan_aligned16(qkv) && scan_aligned16(ag) && Cq % 4 == 0 && ldag % 4 == 0 && d % 4 == 0 && dv % 4 == 0 &&
+                    vt % 4 == 0;
+    XB_SCAN_DISPATCH(delta_rule_kernel, ds, o, qkv, Cq, proj, ldp, beta_off, ag, ldag, dt_bias, A_log, state, q_start, slots, H,
+                     G, d, dv, unit_eps, tt, stage, warps, vec)
     return xb_launch_status();
 }
 
