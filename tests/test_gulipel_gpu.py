@@ -246,6 +246,38 @@ def test_short_convolution_over_portions_and_batches(K, bias):
         assert torch.isnan(state[2]).all()                # a slot of no request is not touched
 
 
+@pytest.mark.parametrize("C,off,width", [(48, 8, 64), (45, 7, 60), (130, 0, 130)])
+@pytest.mark.parametrize("K", [2, 4, 8])
+def test_short_convolution_over_long_runs_of_tokens(K, C, off, width):
+    """Thousands of tokens in a step, so that a thread walks a run of tokens with the inputs before it in registers:
+    runs that start in the middle of a request, runs that cross from one request into the next one's first tokens,
+    a portion that ends inside a run, channels in fours and one by one; the same numbers as a step of few tokens."""
+    k = _k()
+    lens = [3011, 1702, 95]
+    taps, b = _rand(C, K, seed=3).float(), _rand(C, seed=4).float()
+    us = [_rand(n, width, seed=20 + n).float() for n in lens]
+    want = [plain.silu(plain.causal_conv(u.double()[:, off:off + C], taps.double(), b.double())) for u in us]
+    slots = [2, 0, 1]
+    state = torch.zeros((3, K - 1, C), device=DEV)
+    got = [torch.zeros(n, C, dtype=F64) for n in lens]
+    for step in _steps_of([[2990, 21], [1702], [3, 92]]):
+        q_start, req, _, sl = _meta(step, slots)
+        u = torch.cat([us[r][s:s + n] for r, s, n in step]).to(DEV)
+        y = torch.full((u.shape[0], C), float("nan"), device=DEV)
+        k.conv_silu(y, u, off, taps.to(DEV), b.to(DEV), state, req, q_start, sl, len(step))
+        at = 0
+        for r, s, n in step:
+            got[r][s:s + n] = y[at:at + n].double().cpu()
+            at += n
+    for g, wnt in zip(got, want):
+        _close(g, wnt, 1e-5)
+    # a short step of the same tokens gives the same bits: the taps are added in one order
+    q_start, req, _, sl = _meta([(2, 0, 40)], slots)
+    y_short = torch.empty(40, C, device=DEV)
+    k.conv_silu(y_short, us[2][:40].to(DEV), off, taps.to(DEV), b.to(DEV), torch.zeros_like(state), req, q_start, sl, 1)
+    assert torch.equal(y_short.double().cpu(), got[2][:40])
+
+
 # ---------------------------------------------------------------------------------------------
 # the state-space scan
 # ---------------------------------------------------------------------------------------------
@@ -413,7 +445,9 @@ def test_delta_rule_reads_its_own_write_and_keeps_it_for_hundreds_of_tokens():
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,groups,part,w_len", [(5, 3, 8, 8), (40, 2, 96, 192), (7, 1, 1500, 1500), (9, 6, 20, 20), (3, 4, 7, 28)])
+@pytest.mark.parametrize("T,groups,part,w_len", [(5, 3, 8, 8), (40, 2, 96, 192), (7, 1, 1500, 1500), (9, 6, 20, 20), (3, 4, 7, 28),
+                                                 (11, 5, 50, 50), (6, 3, 200, 600), (4, 2, 512, 512), (3, 2, 516, 516),
+                                                 (700, 9, 128, 128)])
 def test_gate_and_norm_over_groups_of_channels(out_dtype, T, groups, part, w_len):
     k = _k()
     W = groups * part

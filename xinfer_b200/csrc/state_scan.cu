@@ -490,17 +490,74 @@ __global__ void gated_head_norm_kernel(TO* __restrict__ out, const float* __rest
     }
 }
 
+// The same for parts of at most 32 * NV channels: a warp per (token, part) keeps its channels in registers, one pass
+// over memory, sums by shuffles; a block's warps take neighbouring parts of a token.
+template <typename TO, int NV>
+__global__ void __launch_bounds__(256) gated_head_norm_warp_kernel(TO* __restrict__ out, const float* __restrict__ y,
+                                                                   const float* __restrict__ gate, long long ldg, int g_off,
+                                                                   const float* __restrict__ w, int w_len, int W, int part,
+                                                                   float eps, int mode, long long units) {
+    const int lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= units) return;
+    const int parts = W / part;
+    const long long t = unit / parts;
+    const int c0 = (int)(unit % parts) * part;
+    const float* yr = y + (size_t)t * W + c0;
+    const float* gr = gate + (size_t)t * ldg + g_off + c0;
+    float v[NV], z[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = lane + 32 * k;
+        v[k] = i < part ? yr[i] : 0.f;
+        z[k] = i < part ? gr[i] : 0.f;
+        if (mode == 0) v[k] *= z[k] / (1.f + expf(-z[k]));
+        ss = fmaf(v[k], v[k], ss);
+    }
+    const float inv = 1.f / sqrtf(warp_total(ss) / (float)part + eps);
+    TO* o = out + (size_t)t * W + c0;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int i = lane + 32 * k;
+        if (i >= part) continue;
+        float r = v[k] * inv * w[(c0 + i) % w_len];
+        if (mode != 0) r *= sigmoid_exact(z[k]);
+        o[i] = from_f32<TO>(r);
+    }
+}
+
+template <typename TO>
+static void gated_head_norm_launch(TO* out, const float* y, const float* gate, long long ldg, int g_off, const float* w,
+                                   int w_len, int tokens, int W, int part, float eps, int mode, cudaStream_t stream) {
+    const long long units = (long long)tokens * (W / part);
+    const int warps = 8;
+    const unsigned blocks = (unsigned)((units + warps - 1) / warps);
+#define XB_HEAD_NORM_NV(NVV)                                                                                              \
+    gated_head_norm_warp_kernel<TO, NVV><<<blocks, warps * 32, 0, stream>>>(out, y, gate, ldg, g_off, w, w_len, W, part, \
+                                                                            eps, mode, units)
+    if (part <= 32) XB_HEAD_NORM_NV(1);
+    else if (part <= 64) XB_HEAD_NORM_NV(2);
+    else if (part <= 128) XB_HEAD_NORM_NV(4);
+    else if (part <= 256) XB_HEAD_NORM_NV(8);
+    else if (part <= 512) XB_HEAD_NORM_NV(16);
+    else {
+        const dim3 grid(tokens, W / part);
+        const int threads = part >= 1024 ? 256 : 128;
+        gated_head_norm_kernel<TO><<<grid, threads, 0, stream>>>(out, y, gate, ldg, g_off, w, w_len, W, part, eps, mode);
+    }
+#undef XB_HEAD_NORM_NV
+}
+
 XB_EXPORT int xb_gated_head_norm(int out_dtype, void* out, const float* y, const float* gate, long long ldg, int g_off,
                                  const float* w, int w_len, int tokens, int W, int part, float eps, int mode,
                                  cudaStream_t stream) {
     if (tokens <= 0 || W <= 0) return 0;
     if (part <= 0 || W % part || W / part > 65535) return (int)cudaErrorInvalidValue;
-    const dim3 grid(tokens, W / part);
-    const int threads = part >= 1024 ? 256 : (part >= 128 ? 128 : (part > 32 ? 64 : 32));
     if (out_dtype == XB_F32)
-        gated_head_norm_kernel<float><<<grid, threads, 0, stream>>>((float*)out, y, gate, ldg, g_off, w, w_len, W, part, eps, mode);
+        gated_head_norm_launch<float>((float*)out, y, gate, ldg, g_off, w, w_len, tokens, W, part, eps, mode, stream);
     else
-        gated_head_norm_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16*)out, y, gate, ldg, g_off, w, w_len,
-                                                                           W, part, eps, mode);
+        gated_head_norm_launch<__nv_bfloat16>((__nv_bfloat16*)out, y, gate, ldg, g_off, w, w_len, tokens, W, part, eps, mode,
+                                              stream);
     return xb_launch_status();
 }

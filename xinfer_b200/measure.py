@@ -675,6 +675,18 @@ def gulipel_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
            "float32 residual sum + norm", tokens=T)
     del xs, bs, os_, ds
 
+    # the like kernels of the small ones: the SiLU gate and the residual sum + RMSNorm of a bfloat16 stream
+    gus = [torch.randn(T, 2 * intermediate, device=device).bfloat16() for _ in range(sets)]
+    acts = [torch.empty(T, intermediate, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    record("like: SiLU gate", 3 * T * intermediate * 2, lambda i: kernels.swiglu(acts[i], gus[i]), tokens=T)
+    del gus, acts
+    hs = [torch.randn(T, hidden, device=device).bfloat16() for _ in range(sets)]
+    rs = [torch.randn(T, hidden, device=device).bfloat16() for _ in range(sets)]
+    ns = [torch.empty(T, hidden, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    record("like: residual sum + RMSNorm", 4 * T * hidden * 2,
+           lambda i: kernels.rmsnorm(ns[i], hs[i], w, 1e-6, err, branch=rs[i], sum_out=hs[i]), tokens=T)
+    del hs, rs, ns
+
     # the like kernel of the scans: Tidarax's gated recurrence (a vector state per channel) over the same prompt
     W = hidden
     zxgs = [f32(T, 3 * W) for _ in range(sets)]
