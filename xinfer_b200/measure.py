@@ -601,7 +601,8 @@ def gulipel_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
 
     def record(name, nbytes, run, like=None, flops=0.0, n=sets, **more):
-        us = _loop_time_us(lambda: [run(i) for i in range(n)]) / n
+        # replayed from a CUDA graph: several of these kernels are shorter than the host's share of a launch
+        us = _graph_time_us(lambda: [run(i) for i in range(n)], n)
         rec = {"kernel": name, "bytes": nbytes, "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1)}
         floor_us = nbytes / (hbm_gbs or 6650.0) / 1e3
         if flops:
