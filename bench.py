@@ -266,15 +266,15 @@ def gulipel_config(z: dict, layers: int, vocab: int, max_positions: int) -> dict
     dense = dict(kind="dense", ff=z["intermediate"])
     ssm = dict(heads=g["ss_heads"], vdim=g["ss_head_dim"], state=g["ss_state"], groups=g["ss_groups"], conv=g["conv"],
                norm_groups=g["ss_groups"])
-    par = dict(left=dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, q_temp=dict(coef=0.3, every=256)),
+    par = dict(left=dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, q_temp=dict(coef=0.25, every=512)),
                right=dict(heads=g["delta_heads"], kv_heads=g["delta_kv_heads"], dim=g["delta_dim"], vdim=g["delta_vdim"], conv=g["conv"],
                           decay_rank=g["rank"], gate_rank=g["rank"]))
     # state-space layers with a parallel layer every other one: as many attention layers per model as a Tidarax
     # model of half the depth, the rest recurrent
     out = [dict(type="parallel", mixer=par, mlp=dense) if i % 2 == 1 else dict(type="mamba2" if i % 4 == 0 else "mamba2_2", mixer=ssm, mlp=dense)
            for i in range(layers)]
-    return dict(architecture="Gulipel", vocab=vocab, width=z["hidden"], norm=dict(eps=1e-5), max_positions=max_positions,
-                logit_softcap=30.0, embedding=dict(scale=z["hidden"] ** 0.5, bigram=dict(buckets=100003, mul_prev=127, mul_cur=17)),
+    return dict(architecture="Gulipel", vocab=vocab, width=z["hidden"], norm=dict(eps=1e-6), max_positions=max_positions,
+                logit_softcap=50.0, embedding=dict(scale=z["hidden"] ** 0.5, bigram=dict(buckets=100003, mul_prev=8191, mul_cur=31)),
                 token_side=dict(dim=64), layers=out)
 
 

@@ -43,7 +43,7 @@ def silu(z: torch.Tensor) -> torch.Tensor:
 
 
 def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x[n, C], taps[C, K]: y[t, c] = sum_j taps[c, j] x[t - (K-1) + j, c] (+ bias), zeros before the start."""
+    """x[n, C], taps[C, K]: y[t, c] = sum_j taps[c, j] x[t - (K-1) + j, c] (+ bias); inputs before the first row count as zero."""
     n, C = x.shape
     K = taps.shape[1]
     padded = torch.cat([torch.zeros(K - 1, C, dtype=x.dtype), x], dim=0)

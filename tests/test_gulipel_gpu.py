@@ -215,7 +215,7 @@ def test_token_gate_reads_the_layers_own_columns(dtype):
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("K,bias", [(1, False), (2, True), (3, False), (4, True), (5, True), (9, False)])
 def test_short_convolution_over_portions_and_batches(K, bias):
-    """Portions shorter than the taps (one and two tokens), first tokens (zeros before the start), requests side
+    """Portions shorter than the taps (one and two tokens), first tokens (nothing but zeros behind them), requests side
     by side, slots that held another request's inputs."""
     k = _k()
     C, off, width = 45, 7, 60

@@ -2,7 +2,7 @@
 //
 //   selective_scan_kernel   (state-space duality)   S[N, P]:  S <- exp(-A dt) S + dt B x^T,   y = S^T C + D x
 //   delta_rule_kernel       (gated delta rule)      S[d, dv]: S <- diag(g) S,  u = beta (v - S^T k),  S <- S + k u^T,
-//                                                             o = S^T q      (the read-out sees the token's own write)
+//                                                             o = S^T q      (read after the token's own update)    
 //   gated_head_norm_kernel  the gate and the RMS norm over a head (or a group of channels) behind either
 //
 // Layout of both scans: a block takes one (request, head) and a tile of the state's columns (columns never mix).

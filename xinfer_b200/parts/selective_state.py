@@ -5,7 +5,7 @@
     dt <- softplus(dt + dt_bias)
     S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T       per head, S of state x head_dim, zero at a sequence's start
     y_t = S_t^T C_t + D x_t
-    out = W_o ( rms_norm_in_parts(y * silu(z)) * w )       the gate comes before the norm
+    out = W_o ( rms_norm_in_parts(y * silu(z)) * w )       gated first, normed second
 
 The projection leaves float32; the convolution, the step sizes, the decays, the state and the gated norm are
 float32 in both engine types.  A request keeps the state matrices and the convolution's last inputs in its row of
