@@ -374,12 +374,13 @@ static inline int scan_row_groups(int rows) {
 }
 
 // Computing warps per block: enough to cover the columns (at most 8), fewer (down to 2) while the grid would
-// leave processors idle.
+// leave a third of the processors idle.  Every block of a head repeats the feeding warps' work, so column tiles
+// are not cut finer than that.
 static inline int scan_warps(int cols, int ds, long long heads_total) {
     const int per_warp = (32 / ds) * 2;
     int warps = 1;
     while (warps < 8 && warps * per_warp < cols) warps *= 2;
-    while (warps > 2 && heads_total * ((cols + warps * per_warp - 1) / (warps * per_warp)) < 148) warps /= 2;
+    while (warps > 2 && heads_total * ((cols + warps * per_warp - 1) / (warps * per_warp)) < 100) warps /= 2;
     return warps;
 }
 
@@ -429,7 +430,7 @@ XB_EXPORT int xb_selective_scan(float* y, const float* xbc, int C, const float* 
     size_t bytes;
     scan_tile(2, ds, vt, tt, stage, bytes);
     const dim3 grid(entries, H, (P + vt - 1) / vt);
-    const int threads = (warps + 2) * 32;  // two feeding warps
+    const int threads = (warps + 4) * 32;  // four feeding warps
     const int vec = scan_aligned16(xbc) && C % 4 == 0 && P % 4 == 0 && N % 4 == 0 && vt % 4 == 0;
     XB_SCAN_DISPATCH(selective_scan_kernel, ds, y, xbc, C, proj, ldp, dt_off, dt_bias, A_log, Dv, state, q_start, slots, H, P, N,
                      G, tt, stage, warps, vec)
@@ -448,7 +449,8 @@ XB_EXPORT int xb_delta_rule(float* o, const float* qkv, int Cq, const float* pro
     size_t bytes;
     scan_tile(3, ds, vt, tt, stage, bytes);
     const dim3 grid(entries, H, (dv + vt - 1) / vt);
-    const int threads = (warps + 4) * 32;  // four feeding warps: the unit vectors and decays are theirs
+    // the unit vectors and decays are the feeding warps' work: eight of them where the block has room, else four
+    const int threads = (warps + (warps <= 4 ? 8 : 4)) * 32;
     const int vec = scan_aligned16(qkv) && scan_aligned16(ag) && Cq % 4 == 0 && ldag % 4 == 0 && d % 4 == 0 && dv % 4 == 0 &&
                     vt % 4 == 0;
     XB_SCAN_DISPATCH(delta_rule_kernel, ds, o, qkv, Cq, proj, ldp, beta_off, ag, ldag, dt_bias, A_log, state, q_start, slots, H,
