@@ -147,8 +147,8 @@ XB_EXPORT int xb_add(int dtype, void* out, const void* x, const void* branch, lo
 
 // ------------------------------------------------------------------------------------------
 // Plain matrix product  out[M, N] = a[M, K] . w[N, K]^T  with float32 FMA accumulation.
-// 64x64 tile, 16-deep panels, 256 threads with 4x4 outputs each.  k runs in order for every
-// output, so a row's result does not depend on M.
+// 64x64 tile, 16-deep panels, 256 threads with 4x4 outputs each.  Every output sums its panels' terms in
+// order and the panels' sums in order, so a row's result does not depend on M.
 // ------------------------------------------------------------------------------------------
 template <typename TA, typename TW, typename TO>
 __global__ void gemm_plain_kernel(TO* __restrict__ out, const TA* __restrict__ a,
@@ -175,6 +175,13 @@ __global__ void gemm_plain_kernel(TO* __restrict__ out, const TA* __restrict__ a
             sw[c][r] = (gn < N && gk < K) ? to_f32<TW>(w[(size_t)gn * K + gk]) : 0.f;
         }
         __syncthreads();
+        // a tile's BK terms are summed on their own and then added to the total: the rounding of a long sum grows
+        // with the number of tiles rather than with K
+        float part[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
             float av[4], wv[4];
@@ -185,8 +192,12 @@ __global__ void gemm_plain_kernel(TO* __restrict__ out, const TA* __restrict__ a
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) part[i][j] = fmaf(av[i], wv[j], part[i][j]);
         }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
         __syncthreads();
     }
 #pragma unroll
