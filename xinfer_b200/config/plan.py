@@ -138,6 +138,23 @@ class AttentionSpec(PartSpec):
     q_temp: Optional[Tuple[float, int]] = None
     # the concatenated heads are multiplied by sigmoid(W_g h) before the output projection; the name of W_g
     gate_name: Optional[str] = None
+    # the gate is one number per head (W_g has ``num_heads`` rows) instead of one per channel
+    gate_per_head: bool = False
+    # the keys as projected (with their bias, before norm and rotation) double as values: there is no W_v
+    value_from_key: bool = False
+    # q/k norm with ONE root mean square over the whole q projection (and one over the whole k projection) and
+    # weights of that size, instead of one per head
+    qk_norm_whole: bool = False
+    # the output projection has a bias too (its matrix's name with ``bias_suffix``)
+    out_bias: bool = False
+    # scores pass cap * tanh(score / cap) before the softmax
+    score_softcap: Optional[float] = None
+    # a distance bias after the cap: head h's score of a key ``dist`` positions back loses
+    # 2^(-x (h + 1) / num_heads) * dist, x this exponent
+    distance_slope_exponent: Optional[float] = None
+    # a query sees the earlier keys of its own chunk of this many positions (chunks counted from position 0 of the
+    # sequence) instead of a window
+    chunk: Optional[int] = None
 
     @property
     def value_dim(self) -> int:
@@ -258,6 +275,32 @@ class FeedForwardSpec(PartSpec):
     names: Optional[Tuple[str, ...]] = None
     # the three projections have biases: the matrix's name with this suffix (None: no biases)
     bias_suffix: Optional[str] = None
+    # parameters of activations that take some ("swish_clamp": limit, alpha)
+    act_params: Tuple[float, ...] = ()
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec(PartSpec):
+    """``experts`` small gated feed-forwards (``e0.``, ``e1.``, ... after the prefix, without biases) of which a
+    learned router gives every token ``top``.  Scores are ``sigmoid(W_router h)`` in float32; the choice is made
+    on ``score + correction`` (a learned vector; ``correction`` False: on the scores), the weights are the chosen
+    experts' plain scores (``renormalize``: divided by their sum).  Experts form ``groups`` equal groups of
+    neighbours; a group's score is the sum of its ``group_best`` largest choice scores and only experts of the
+    ``keep`` best groups can be chosen.  ``activation`` / ``act_params`` as in ``FeedForwardSpec``.  ``shared``:
+    a gated feed-forward of its own sizes (``shared.`` after the prefix) that every token runs and that is added."""
+
+    hidden: int = 0
+    intermediate: int = 0
+    experts: int = 0
+    top: int = 1
+    groups: int = 1
+    keep: int = 1
+    group_best: int = 2
+    correction: bool = True
+    renormalize: bool = False
+    activation: str = "silu"
+    act_params: Tuple[float, ...] = ()
+    shared: Optional[FeedForwardSpec] = None
 
 
 @dataclass(frozen=True)
@@ -403,10 +446,12 @@ class PairEmbeddingSpec:
 @dataclass(frozen=True)
 class LayerRun:
     """One execution of a block.  ``cache_from`` names an earlier position in the run list whose
-    cache this run reads instead of writing its own (None = own cache)."""
+    cache this run reads instead of writing its own (None = own cache).  ``add_input``: the embedding's
+    output (the residual stream as it was before the first run) is added to the stream before this run."""
 
     block: int
     cache_from: Optional[int] = None
+    add_input: bool = False
 
 
 @dataclass(frozen=True)

@@ -84,10 +84,12 @@ def _register_builtin() -> None:
     from .tidarax import TidaraxConfig
     from .dufitar import DufitarConfig
     from .gulipel import GulipelConfig
+    from .mikutar import MikutarConfig
     register_architecture(Qwen3Config.ARCHITECTURE, Qwen3Config.from_dict, lambda c: c.plan())
     register_architecture(TidaraxConfig.ARCHITECTURE, TidaraxConfig.from_dict, lambda c: c.plan())
     register_architecture(DufitarConfig.ARCHITECTURE, DufitarConfig.from_dict, lambda c: c.plan())
     register_architecture(GulipelConfig.ARCHITECTURE, GulipelConfig.from_dict, lambda c: c.plan())
+    register_architecture(MikutarConfig.ARCHITECTURE, MikutarConfig.from_dict, lambda c: c.plan())
 
 
 _register_builtin()

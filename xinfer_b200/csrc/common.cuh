@@ -67,20 +67,42 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 // the float32 path divides and exponentiates exactly.
 __device__ __forceinline__ float silu_mul_bf16(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
-// Activations of a gated feed-forward, act(g) * u, by code (shared with the Python side).
+// Activations of a gated feed-forward, act(g) * f(u), by code (shared with the Python side).  Two of them take
+// parameters p0 and p1:
+//   relu           max(g, 0) * u
+//   clamped swish  with a = min(g, p0) and b = clamp(u, -p0, p0):  a * sigmoid(p1 * a) * (b + 1)
 #define XB_ACT_SILU 0
 #define XB_ACT_GELU_TANH 1
+#define XB_ACT_RELU 2
+#define XB_ACT_SWISH_CLAMP 3
 // gelu in its tanh form: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), float32 throughout
 __device__ __forceinline__ float gelu_tanh_f32(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
+__device__ __forceinline__ float swish_clamp_f32(float g, float u, float limit, float alpha) {
+    const float a = fminf(g, limit), b = fminf(fmaxf(u, -limit), limit);
+    return a / (1.f + expf(-alpha * a)) * (b + 1.f);
+}
 template <int ACT>
-__device__ __forceinline__ float gate_mul_bf16(float g, float u) {
+__device__ __forceinline__ float gate_mul_bf16(float g, float u, float p0 = 0.f, float p1 = 0.f) {
+    if (ACT == XB_ACT_RELU) return fmaxf(g, 0.f) * u;
+    if (ACT == XB_ACT_SWISH_CLAMP) return swish_clamp_f32(g, u, p0, p1);
     return ACT == XB_ACT_GELU_TANH ? gelu_tanh_f32(g) * u : silu_mul_bf16(g, u);
 }
 template <int ACT>
-__device__ __forceinline__ float gate_mul_f32(float g, float u) {
+__device__ __forceinline__ float gate_mul_f32(float g, float u, float p0 = 0.f, float p1 = 0.f) {
+    if (ACT == XB_ACT_RELU) return fmaxf(g, 0.f) * u;
+    if (ACT == XB_ACT_SWISH_CLAMP) return swish_clamp_f32(g, u, p0, p1);
     return ACT == XB_ACT_GELU_TANH ? gelu_tanh_f32(g) * u : g / (1.f + expf(-g)) * u;
+}
+// the same by a code known only at run time (epilogues of products, where the branch costs nothing)
+__device__ __forceinline__ float gate_mul_any(int act, float g, float u, float p0, float p1) {
+    switch (act) {
+        case XB_ACT_GELU_TANH: return gelu_tanh_f32(g) * u;
+        case XB_ACT_RELU: return fmaxf(g, 0.f) * u;
+        case XB_ACT_SWISH_CLAMP: return swish_clamp_f32(g, u, p0, p1);
+        default: return g / (1.f + expf(-g)) * u;
+    }
 }
 
 // Last CUDA error of a launch as an int for the caller (0 = ok).

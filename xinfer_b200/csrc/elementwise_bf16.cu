@@ -101,7 +101,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_bf16_kernel(__nv_bfloat16* __res
 constexpr int SWIGLU_THREADS = 128;
 template <int SWIGLU_UNROLL, int ACT>
 __global__ void __launch_bounds__(SWIGLU_THREADS)
-swiglu_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int inter, int tokens) {
+swiglu_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int inter, int tokens, float p0,
+                   float p1) {
     pdl_launch_dependents();
     pdl_wait();
     const int vpr = inter / 8;
@@ -125,7 +126,7 @@ swiglu_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
                 unpack8(pg[k], g);
                 unpack8(pu[k], u);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = gate_mul_bf16<ACT>(g[e], u[e]);
+                for (int e = 0; e < 8; ++e) y[e] = gate_mul_bf16<ACT>(g[e], u[e], p0, p1);
                 reinterpret_cast<Pack8*>(out + (size_t)t * inter)[c] = pack8(y);
             }
         }
@@ -138,7 +139,8 @@ swiglu_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
 constexpr int SG_THREADS = 128, SG_U = 4;
 template <int ACT>
 __global__ void __launch_bounds__(SG_THREADS)
-swiglu_rows_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int inter, int tokens) {
+swiglu_rows_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int inter, int tokens, float p0,
+                        float p1) {
     pdl_launch_dependents();
     pdl_wait();
     const int vpr = inter / 8;
@@ -165,7 +167,7 @@ swiglu_rows_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __
             unpack8(pg[k], g);
             unpack8(pu[k], u);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) y[k][e] = gate_mul_bf16<ACT>(g[e], u[e]);
+            for (int e = 0; e < 8; ++e) y[k][e] = gate_mul_bf16<ACT>(g[e], u[e], p0, p1);
         }
         const int next = t + gridDim.y;
         if (next < tokens) fetch(next);
@@ -229,30 +231,36 @@ XB_EXPORT int xb_rmsnorm_bf16(void* out, void* sum_out, const void* x, const voi
     return (int)cudaErrorInvalidValue;
 }
 
-// act: XB_ACT_SILU or XB_ACT_GELU_TANH (the gate's activation)
+// act: the gate's activation by code, p0 and p1 its parameters
 template <int ACT>
-static int swiglu_bf16_launch(void* out, const void* gu, int tokens, int inter, cudaStream_t stream) {
+static int swiglu_bf16_launch(void* out, const void* gu, int tokens, int inter, float p0, float p1, cudaStream_t stream) {
     const int vpr = inter / 8;
     const unsigned rows = (unsigned)(tokens < 65535 ? tokens : 65535);
     if ((long long)tokens * vpr >= 148LL * 2048 * 2) {
         const int per_block = SWIGLU_THREADS * 4;
         return xb_launch(swiglu_bf16_kernel<4, ACT>, dim3((unsigned)((vpr + per_block - 1) / per_block), rows), dim3(SWIGLU_THREADS), 0,
-                         stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, inter, tokens);
+                         stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, inter, tokens, p0, p1);
     }
     return xb_launch(swiglu_bf16_kernel<1, ACT>, dim3((unsigned)((vpr + SWIGLU_THREADS - 1) / SWIGLU_THREADS), rows), dim3(SWIGLU_THREADS), 0,
-                     stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, inter, tokens);
+                     stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, inter, tokens, p0, p1);
 }
 
-XB_EXPORT int xb_swiglu_bf16(void* out, const void* gu, int tokens, int inter, int act, cudaStream_t stream) {
+XB_EXPORT int xb_swiglu_bf16(void* out, const void* gu, int tokens, int inter, int act, float p0, float p1, cudaStream_t stream) {
     if (tokens <= 0 || inter <= 0) return 0;
     if (inter % 8) return (int)cudaErrorInvalidValue;
-    return act == XB_ACT_GELU_TANH ? swiglu_bf16_launch<XB_ACT_GELU_TANH>(out, gu, tokens, inter, stream)
-                                   : swiglu_bf16_launch<XB_ACT_SILU>(out, gu, tokens, inter, stream);
+    switch (act) {
+        case XB_ACT_SILU: return swiglu_bf16_launch<XB_ACT_SILU>(out, gu, tokens, inter, p0, p1, stream);
+        case XB_ACT_GELU_TANH: return swiglu_bf16_launch<XB_ACT_GELU_TANH>(out, gu, tokens, inter, p0, p1, stream);
+        case XB_ACT_RELU: return swiglu_bf16_launch<XB_ACT_RELU>(out, gu, tokens, inter, p0, p1, stream);
+        case XB_ACT_SWISH_CLAMP: return swiglu_bf16_launch<XB_ACT_SWISH_CLAMP>(out, gu, tokens, inter, p0, p1, stream);
+    }
+    return (int)cudaErrorInvalidValue;
 }
 
-// The SiLU gate for many rows (a prompt portion): about eight blocks per SM stay resident and walk over
+// The gate for many rows (a prompt portion): about eight blocks per SM stay resident and walk over
 // the rows with the next row requested early; the same values as xb_swiglu_bf16.
-XB_EXPORT int xb_swiglu_rows_bf16(void* out, const void* gu, int tokens, int inter, int act, cudaStream_t stream) {
+XB_EXPORT int xb_swiglu_rows_bf16(void* out, const void* gu, int tokens, int inter, int act, float p0, float p1,
+                                  cudaStream_t stream) {
     if (tokens <= 0 || inter <= 0) return 0;
     if (inter % 8) return (int)cudaErrorNotSupported;
     const int vpr = inter / 8;
@@ -261,11 +269,17 @@ XB_EXPORT int xb_swiglu_rows_bf16(void* out, const void* gu, int tokens, int int
     // about eight blocks per SM stay resident and walk over the rows
     unsigned by = (148u * 8u + bx - 1) / bx;
     if (by > (unsigned)tokens) by = (unsigned)tokens;
-    if (act == XB_ACT_GELU_TANH)
-        return xb_launch(swiglu_rows_bf16_kernel<XB_ACT_GELU_TANH>, dim3(bx, by), dim3(SG_THREADS), 0, stream, (__nv_bfloat16*)out,
-                         (const __nv_bfloat16*)gu, inter, tokens);
-    return xb_launch(swiglu_rows_bf16_kernel<XB_ACT_SILU>, dim3(bx, by), dim3(SG_THREADS), 0, stream, (__nv_bfloat16*)out,
-                     (const __nv_bfloat16*)gu, inter, tokens);
+#define XB_SGR(A)                                                                                                         \
+    return xb_launch(swiglu_rows_bf16_kernel<A>, dim3(bx, by), dim3(SG_THREADS), 0, stream, (__nv_bfloat16*)out,          \
+                     (const __nv_bfloat16*)gu, inter, tokens, p0, p1)
+    switch (act) {
+        case XB_ACT_SILU: XB_SGR(XB_ACT_SILU);
+        case XB_ACT_GELU_TANH: XB_SGR(XB_ACT_GELU_TANH);
+        case XB_ACT_RELU: XB_SGR(XB_ACT_RELU);
+        case XB_ACT_SWISH_CLAMP: XB_SGR(XB_ACT_SWISH_CLAMP);
+    }
+#undef XB_SGR
+    return (int)cudaErrorInvalidValue;
 }
 
 // Needs d a multiple of 16 (at most 512) and, for the NeoX layout, rot == d.

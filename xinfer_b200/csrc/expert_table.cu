@@ -15,6 +15,7 @@
 
 // ------------------------------------------------------------------------------------------
 // 1. route.  One block.  offsets[E + 1]; perm[r] = t * top + k for grouped row r; inv[t * top + k] = r.
+// The experts of token t are row id_t of the table, or row t where no ids are given (a router's choices).
 // Padding tokens (request -1) take part in nothing: their pairs get inv = -1.
 // ------------------------------------------------------------------------------------------
 __global__ void expert_route_kernel(int* __restrict__ offsets, int* __restrict__ perm, int* __restrict__ inv,
@@ -29,7 +30,7 @@ __global__ void expert_route_kernel(int* __restrict__ offsets, int* __restrict__
     const int n = T * top;
     for (int p = threadIdx.x; p < n; p += blockDim.x) {
         const int t = p / top, k = p - t * top;
-        int id = ids[t];
+        int id = ids != nullptr ? ids[t] : t;     // no ids: the table has a row per token of the step
         if (id < 0 && sampled != nullptr && -1 - id < num_sampled) id = sampled[-1 - id];
         int e = -1;
         if (req_of_token[t] >= 0) {
@@ -80,14 +81,14 @@ XB_EXPORT int xb_expert_route(int* offsets, int* perm, int* inv, const int* tabl
 // ------------------------------------------------------------------------------------------
 // 2. grouped product on FMA units.  y[r, n] = sum_k a[src(r), k] * w[e(r), n, k]
 //    gather: src(r) = perm[r] / top, else src(r) = r.
-//    gated:  w[e] is [2 * N, K] (gate rows, then up rows), y[r, n] = silu(gate) * up.
+//    gated:  w[e] is [2 * N, K] (gate rows, then up rows), y[r, n] = act(gate) * f(up), the activation by code.
 // 32 x 64 tile, 16-deep panels, 256 threads with 2 x 4 outputs each (x 2 accumulators when gated).
 // Block (x, y): column tile x; row tile y is found by walking over the experts' counts.
 // ------------------------------------------------------------------------------------------
 template <typename TA, typename TW, typename TO, bool GATED>
 __global__ void expert_gemm_kernel(TO* __restrict__ y, const TA* __restrict__ a, const TW* __restrict__ w,
                                    const int* __restrict__ offsets, const int* __restrict__ perm, int gather, int top,
-                                   int E, int N, int K, long long ldw, long long estride) {
+                                   int E, int N, int K, long long ldw, long long estride, int act, float p0, float p1) {
     constexpr int BM = 32, BN = 64, BK = 16;
     __shared__ float sa[BK][BM + 1];
     __shared__ float sw[GATED ? 2 : 1][BK][BN + 1];
@@ -169,8 +170,7 @@ __global__ void expert_gemm_kernel(TO* __restrict__ y, const TA* __restrict__ a,
             if (gn >= N) continue;
             float v = acc[i][j];
             if (GATED) {
-                const float g = v, u = acc2[i][j];
-                v = g / (1.f + expf(-g)) * u;
+                v = gate_mul_any(act, v, acc2[i][j], p0, p1);
             }
             y[(size_t)(row0 + r) * N + gn] = from_f32<TO>(v);
         }
@@ -179,12 +179,13 @@ __global__ void expert_gemm_kernel(TO* __restrict__ y, const TA* __restrict__ a,
 
 template <typename TA, typename TW, typename TO>
 static int expert_gemm_launch(void* y, const void* a, const void* w, const int* offsets, const int* perm, int gather, int top,
-                              int E, int rows_max, int N, int K, int gated, long long ldw, long long estride, cudaStream_t stream) {
+                              int E, int rows_max, int N, int K, int gated, long long ldw, long long estride, int act, float p0,
+                              float p1, cudaStream_t stream) {
     const dim3 grid((N + 63) / 64, (rows_max + 31) / 32 + E);
     if (gated)
-        expert_gemm_kernel<TA, TW, TO, true><<<grid, 256, 0, stream>>>((TO*)y, (const TA*)a, (const TW*)w, offsets, perm, gather, top, E, N, K, ldw, estride);
+        expert_gemm_kernel<TA, TW, TO, true><<<grid, 256, 0, stream>>>((TO*)y, (const TA*)a, (const TW*)w, offsets, perm, gather, top, E, N, K, ldw, estride, act, p0, p1);
     else
-        expert_gemm_kernel<TA, TW, TO, false><<<grid, 256, 0, stream>>>((TO*)y, (const TA*)a, (const TW*)w, offsets, perm, gather, top, E, N, K, ldw, estride);
+        expert_gemm_kernel<TA, TW, TO, false><<<grid, 256, 0, stream>>>((TO*)y, (const TA*)a, (const TW*)w, offsets, perm, gather, top, E, N, K, ldw, estride, act, p0, p1);
     return xb_launch_status();
 }
 
@@ -192,10 +193,10 @@ static int expert_gemm_launch(void* y, const void* a, const void* w, const int* 
 // at w + e * estride + n * ldw (elements): [experts, rows, K] blocks, or matrices side by side along K.
 XB_EXPORT int xb_expert_gemm(int in_dtype, int out_dtype, void* y, const void* a, const void* w, const int* offsets,
                              const int* perm, int gather, int top, int experts, int rows_max, int N, int K, int gated,
-                             long long ldw, long long estride, cudaStream_t stream) {
+                             long long ldw, long long estride, int act, float p0, float p1, cudaStream_t stream) {
     if (rows_max <= 0 || N <= 0) return 0;
     typedef __nv_bfloat16 bf;
-#define XB_ARGS y, a, w, offsets, perm, gather, top, experts, rows_max, N, K, gated, ldw, estride, stream
+#define XB_ARGS y, a, w, offsets, perm, gather, top, experts, rows_max, N, K, gated, ldw, estride, act, p0, p1, stream
     if (in_dtype == XB_F32) return out_dtype == XB_F32 ? expert_gemm_launch<float, float, float>(XB_ARGS) : (int)cudaErrorInvalidValue;
     return out_dtype == XB_F32 ? expert_gemm_launch<bf, bf, float>(XB_ARGS) : expert_gemm_launch<bf, bf, bf>(XB_ARGS);
 #undef XB_ARGS
@@ -208,47 +209,51 @@ XB_EXPORT int xb_expert_gemm(int in_dtype, int out_dtype, void* y, const void* a
 //                     = 0                                                       otherwise
 // so that ONE product with the down matrices side by side along K sums the token's experts.
 // ------------------------------------------------------------------------------------------
+// `weights` [T, top] (absent: every chosen expert weighs 1 / top); no ids: the table has a row per token.
 template <typename T>
 __global__ void expert_select_gate_kernel(T* __restrict__ act, const T* __restrict__ gu, const int* __restrict__ table,
                                           const int* __restrict__ ids, const int* __restrict__ sampled, int num_sampled,
                                           const int* __restrict__ req_of_token, int top, int E, int F, int vocab,
-                                          float weight, int* err) {
+                                          float weight, const float* __restrict__ weights, int code, float p0, float p1,
+                                          int* err) {
     const int t = blockIdx.x, e = blockIdx.y;
-    int id = ids[t];
+    int id = ids != nullptr ? ids[t] : t;
     if (id < 0 && sampled != nullptr && -1 - id < num_sampled) id = sampled[-1 - id];
     bool chosen = false;
     if (req_of_token[t] >= 0) {
         if (id < 0 || id >= vocab) {
             if (threadIdx.x == 0 && e == 0) atomicOr(err, XB_ERR_BAD_TOKEN);
         } else {
-            for (int k = 0; k < top; ++k) chosen |= table[(size_t)id * top + k] == e;
+            for (int k = 0; k < top; ++k)
+                if (table[(size_t)id * top + k] == e) {
+                    chosen = true;
+                    if (weights != nullptr) weight = weights[(size_t)id * top + k];
+                }
         }
     }
     const T* g = gu + ((size_t)t * E + e) * 2 * F;
     T* o = act + ((size_t)t * E + e) * F;
     for (int f = threadIdx.x; f < F; f += blockDim.x) {
         float v = 0.f;
-        if (chosen) {
-            const float a = to_f32<T>(g[f]), u = to_f32<T>(g[F + f]);
-            v = a / (1.f + expf(-a)) * u * weight;
-        }
+        if (chosen) v = gate_mul_any(code, to_f32<T>(g[f]), to_f32<T>(g[F + f]), p0, p1) * weight;
         o[f] = from_f32<T>(v);
     }
 }
 
 XB_EXPORT int xb_expert_select_gate(int dtype, void* act, const void* gu, const int* table, const int* ids, const int* sampled,
                                     int num_sampled, const int* req_of_token, int tokens, int top, int experts, int F, int vocab,
-                                    int* err, cudaStream_t stream) {
+                                    const float* weights, int code, float p0, float p1, int* err, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     const dim3 grid(tokens, experts);
     const float weight = 1.f / (float)top;
     if (dtype == XB_F32)
         expert_select_gate_kernel<float><<<grid, 256, 0, stream>>>((float*)act, (const float*)gu, table, ids, sampled, num_sampled,
-                                                                   req_of_token, top, experts, F, vocab, weight, err);
+                                                                   req_of_token, top, experts, F, vocab, weight, weights, code,
+                                                                   p0, p1, err);
     else
         expert_select_gate_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)act, (const __nv_bfloat16*)gu, table, ids,
                                                                            sampled, num_sampled, req_of_token, top, experts, F,
-                                                                           vocab, weight, err);
+                                                                           vocab, weight, weights, code, p0, p1, err);
     return xb_launch_status();
 }
 
@@ -283,29 +288,33 @@ XB_EXPORT int xb_expert_gather(int dtype, void* out, const void* x, const int* p
 }
 
 // ------------------------------------------------------------------------------------------
-// 3. combine.  out[t, :] = (1 / top) * sum_k y[inv[t * top + k], :]   (a pair without a row adds nothing)
+// 3. combine.  out[t, :] = base[t, :] + sum_k w(t, k) * y[inv[t * top + k], :]   (a pair without a row adds nothing)
+// w(t, k) = weights[t * top + k], or 1 / top for all where no weights are given; base may be absent.
 // ------------------------------------------------------------------------------------------
 template <typename TO>
 __global__ void expert_combine_kernel(TO* __restrict__ out, const float* __restrict__ y, const int* __restrict__ inv, int top,
-                                      int N, float weight) {
+                                      int N, float weight, const float* __restrict__ weights, const TO* __restrict__ base) {
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < N; c += blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < top; ++k) {
             const int r = inv[t * top + k];
-            if (r >= 0) s += y[(size_t)r * N + c];
+            if (r >= 0) s += (weights != nullptr ? weights[t * top + k] : 1.f) * y[(size_t)r * N + c];
         }
-        out[(size_t)t * N + c] = from_f32<TO>(s * weight);
+        s *= weight;
+        if (base != nullptr) s += to_f32<TO>(base[(size_t)t * N + c]);
+        out[(size_t)t * N + c] = from_f32<TO>(s);
     }
 }
 
 XB_EXPORT int xb_expert_combine(int out_dtype, void* out, const float* y, const int* inv, int tokens, int top, int N,
-                                cudaStream_t stream) {
+                                const float* weights, const void* base, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    const float weight = 1.f / (float)top;
+    const float weight = weights != nullptr ? 1.f : 1.f / (float)top;
     if (out_dtype == XB_F32)
-        expert_combine_kernel<float><<<tokens, 256, 0, stream>>>((float*)out, y, inv, top, N, weight);
+        expert_combine_kernel<float><<<tokens, 256, 0, stream>>>((float*)out, y, inv, top, N, weight, weights, (const float*)base);
     else
-        expert_combine_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((__nv_bfloat16*)out, y, inv, top, N, weight);
+        expert_combine_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((__nv_bfloat16*)out, y, inv, top, N, weight, weights,
+                                                                         (const __nv_bfloat16*)base);
     return xb_launch_status();
 }

@@ -1,7 +1,7 @@
 // The grouped product of the table-routed experts (see expert_table.cu) for bfloat16 on tensor cores:
 // y[r] = a[src(r)] . w[e(r)]^T over rows grouped by expert, mma.sync m16n8k16 tiles with float32 accumulators.
 // A block takes 128 rows of ONE expert and 128 rows of that expert's matrix (gated: 64 columns of gate and the
-// same 64 of up, finished as silu(gate) * up in the accumulators); K runs in panels of 32 through three
+// same 64 of up, finished as act(gate) * f(up) in the accumulators, the activation by code); K runs in panels of 32 through three
 // shared-memory stages filled by 16-byte asynchronous copies.  A row's sum runs over K in the same order
 // whatever shares its tile, so a token's result does not depend on its company.
 #include "common.cuh"
@@ -19,7 +19,8 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
                                                                      const __nv_bfloat16* __restrict__ w,
                                                                      const int* __restrict__ offsets,
                                                                      const int* __restrict__ perm, int gather, int top, int E,
-                                                                     int N, int K, long long ldw, long long estride) {
+                                                                     int N, int K, long long ldw, long long estride, int act,
+                                                                     float p0, float p1) {
     extern __shared__ __align__(16) unsigned char eg_smem[];
     typedef __nv_bfloat16 (*Tile)[EG_BM][EG_LD];            // EG_BM == EG_BN
     Tile As = reinterpret_cast<Tile>(eg_smem);
@@ -123,7 +124,7 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
                         const int col = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + c;
                         if (col < N) {
                             const float g = acc[i][j][half * 2 + c], u = acc[i][4 + j][half * 2 + c];
-                            yr[col] = from_f32<TO>(g / (1.f + expf(-g)) * u);
+                            yr[col] = from_f32<TO>(gate_mul_any(act, g, u, p0, p1));
                         }
                     }
             } else {
@@ -141,7 +142,7 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
 // bfloat16 operands, K a multiple of 8 (16-byte copies); returns cudaErrorNotSupported for other sizes.
 XB_EXPORT int xb_expert_gemm_mma(int out_dtype, void* y, const void* a, const void* w, const int* offsets, const int* perm,
                                  int gather, int top, int experts, int rows_max, int N, int K, int gated, long long ldw,
-                                 long long estride, cudaStream_t stream) {
+                                 long long estride, int act, float p0, float p1, cudaStream_t stream) {
     if (rows_max <= 0 || N <= 0) return 0;
     if (K % 8 || ldw % 8 || estride % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorNotSupported;
     typedef __nv_bfloat16 bf;
@@ -151,7 +152,8 @@ XB_EXPORT int xb_expert_gemm_mma(int out_dtype, void* y, const void* a, const vo
     do {                                                                                                                      \
         cudaFuncSetAttribute(expert_gemm_mma_kernel<TO, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)EG_SMEM);       \
         expert_gemm_mma_kernel<TO, G><<<grid, EG_THREADS, EG_SMEM, stream>>>((TO*)y, (const bf*)a, (const bf*)w, offsets, perm, \
-                                                                            gather, top, experts, N, K, ldw, estride);        \
+                                                                            gather, top, experts, N, K, ldw, estride, act,    \
+                                                                            p0, p1);                                          \
     } while (0)
     if (out_dtype == XB_F32) {
         if (gated) XB_EG(float, true); else XB_EG(float, false);

@@ -378,6 +378,11 @@ XB_EXPORT int xb_qk_norm_rope_write(
 // elements after the row before it, so keys and values may be columns of one cached row (a latent
 // vector whose first dv channels are the value).  A query row starts at q + t * q_ts + h * q_hs.
 // `sink` (per head, nullable): one more softmax entry of that score that carries no value.
+// Three changes of the score and the mask, each off at 0:
+//   softcap   s <- softcap * tanh(s / softcap)
+//   slope_exp s <- s - 2^(-slope_exp (h + 1) / heads) * (p - j)      (after the cap: a bias on the distance)
+//   chunk     instead of a window: the keys of the query's own chunk of `chunk` positions, counted from
+//             position 0 of the sequence: floor(p / chunk) * chunk .. p
 // ------------------------------------------------------------------------------------------
 template <typename T, int MAXE>
 __global__ void attention_plain_kernel(
@@ -385,7 +390,8 @@ __global__ void attention_plain_kernel(
     const T* __restrict__ v_cache, int k_stride, int v_stride, const float* __restrict__ sink,
     const int* __restrict__ positions,
     const int* __restrict__ req_of_token, const int* __restrict__ block_table, int table_stride,
-    int nh, int nkv, int d, int dv, int page_size, int num_pages, int window, float scale, int* err) {
+    int nh, int nkv, int d, int dv, int page_size, int num_pages, int window, float scale, float softcap, float slope_exp,
+    int chunk, int* err) {
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31;
     const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -412,7 +418,9 @@ __global__ void attention_plain_kernel(
         m = sink[h];
         l = 1.f;
     }
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
+    const float slope = slope_exp > 0.f ? exp2f(-slope_exp * (float)(h + 1) / (float)nh) : 0.f;
     for (int j = lo; j <= pos; ++j) {
         const int page = table[j / page_size];
         if (page < 0 || page >= num_pages) {
@@ -429,6 +437,8 @@ __global__ void attention_plain_kernel(
             if (i < d) s = fmaf(qr[e], to_f32<T>(kr[i]), s);
         }
         s = warp_sum(s);
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+        s -= slope * (float)(pos - j);
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first key
         const float p = expf(s - m_new);
@@ -454,14 +464,15 @@ static int attention_plain_launch(void* out, const void* q, long long q_ts, long
                                   int k_stride, int v_stride, const float* sink,
                                   const int* positions, const int* req_of_token, const int* block_table,
                                   int table_stride, int tokens, int nh, int nkv, int d, int dv, int page_size,
-                                  int num_pages, int window, float scale, int* err, cudaStream_t stream) {
+                                  int num_pages, int window, float scale, float softcap, float slope_exp, int chunk, int* err,
+                                  cudaStream_t stream) {
     dim3 grid(tokens, (nh + 3) / 4);
     const int dm = d > dv ? d : dv;
 #define XB_ATT(MAXE)                                                                              \
     attention_plain_kernel<T, MAXE><<<grid, 128, 0, stream>>>(                                    \
         (T*)out, (const T*)q, q_ts, q_hs, (const T*)kc, (const T*)vc, k_stride, v_stride, sink,  \
         positions, req_of_token, block_table,                                                    \
-        table_stride, nh, nkv, d, dv, page_size, num_pages, window, scale, err)
+        table_stride, nh, nkv, d, dv, page_size, num_pages, window, scale, softcap, slope_exp, chunk, err)
     if (dm <= 64) XB_ATT(2);
     else if (dm <= 128) XB_ATT(4);
     else if (dm <= 256) XB_ATT(8);
@@ -477,16 +488,16 @@ XB_EXPORT int xb_attention_plain(int dtype, void* out, const void* q, long long 
                                  const void* v_cache, int k_stride, int v_stride, const float* sink,
                                  const int* positions, const int* req_of_token,
                                  const int* block_table, int table_stride, int tokens, int nh, int nkv,
-                                 int d, int dv, int page_size, int num_pages, int window, float scale, int* err,
-                                 cudaStream_t stream) {
+                                 int d, int dv, int page_size, int num_pages, int window, float scale, float softcap,
+                                 float slope_exp, int chunk, int* err, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (dtype == XB_F32)
         return attention_plain_launch<float>(out, q, q_ts, q_hs, k_cache, v_cache, k_stride, v_stride, sink, positions,
                                              req_of_token, block_table,
-                                             table_stride, tokens, nh, nkv, d, dv, page_size, num_pages, window, scale, err, stream);
+                                             table_stride, tokens, nh, nkv, d, dv, page_size, num_pages, window, scale, softcap, slope_exp, chunk, err, stream);
     return attention_plain_launch<__nv_bfloat16>(out, q, q_ts, q_hs, k_cache, v_cache, k_stride, v_stride, sink, positions,
                                                  req_of_token, block_table,
-                                                 table_stride, tokens, nh, nkv, d, dv, page_size, num_pages, window, scale, err, stream);
+                                                 table_stride, tokens, nh, nkv, d, dv, page_size, num_pages, window, scale, softcap, slope_exp, chunk, err, stream);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -494,27 +505,37 @@ XB_EXPORT int xb_attention_plain(int dtype, void* out, const void* q, long long 
 // gelu in its tanh form.
 // ------------------------------------------------------------------------------------------
 template <typename T, int ACT>
-__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, size_t n) {
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, size_t n, float p0, float p1) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const size_t t = i / inter, c = i % inter;
     const float g = to_f32<T>(gu[t * 2 * inter + c]);
     const float u = to_f32<T>(gu[t * 2 * inter + inter + c]);
-    out[i] = from_f32<T>(sizeof(T) == 2 ? gate_mul_bf16<ACT>(g, u) : gate_mul_f32<ACT>(g, u));
+    out[i] = from_f32<T>(sizeof(T) == 2 ? gate_mul_bf16<ACT>(g, u, p0, p1) : gate_mul_f32<ACT>(g, u, p0, p1));
 }
 
-XB_EXPORT int xb_swiglu(int dtype, void* out, const void* gu, int tokens, int inter, int act, cudaStream_t stream) {
+XB_EXPORT int xb_swiglu(int dtype, void* out, const void* gu, int tokens, int inter, int act, float p0, float p1,
+                        cudaStream_t stream) {
     const size_t n = (size_t)tokens * inter;
     if (n == 0) return 0;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     typedef __nv_bfloat16 bf;
-    if (dtype == XB_F32) {
-        if (act == XB_ACT_GELU_TANH) swiglu_kernel<float, XB_ACT_GELU_TANH><<<blocks, 256, 0, stream>>>((float*)out, (const float*)gu, inter, n);
-        else swiglu_kernel<float, XB_ACT_SILU><<<blocks, 256, 0, stream>>>((float*)out, (const float*)gu, inter, n);
-    } else {
-        if (act == XB_ACT_GELU_TANH) swiglu_kernel<bf, XB_ACT_GELU_TANH><<<blocks, 256, 0, stream>>>((bf*)out, (const bf*)gu, inter, n);
-        else swiglu_kernel<bf, XB_ACT_SILU><<<blocks, 256, 0, stream>>>((bf*)out, (const bf*)gu, inter, n);
+#define XB_SW(T, A) swiglu_kernel<T, A><<<blocks, 256, 0, stream>>>((T*)out, (const T*)gu, inter, n, p0, p1)
+#define XB_SW_ACT(T)                                            \
+    switch (act) {                                              \
+        case XB_ACT_SILU: XB_SW(T, XB_ACT_SILU); break;         \
+        case XB_ACT_GELU_TANH: XB_SW(T, XB_ACT_GELU_TANH); break; \
+        case XB_ACT_RELU: XB_SW(T, XB_ACT_RELU); break;         \
+        case XB_ACT_SWISH_CLAMP: XB_SW(T, XB_ACT_SWISH_CLAMP); break; \
+        default: return (int)cudaErrorInvalidValue;             \
     }
+    if (dtype == XB_F32) {
+        XB_SW_ACT(float)
+    } else {
+        XB_SW_ACT(bf)
+    }
+#undef XB_SW_ACT
+#undef XB_SW
     return xb_launch_status();
 }
 

@@ -129,16 +129,17 @@ XB_EXPORT int xb_latent_prepare(int dtype, void* q_abs, void* cache, const void*
 }
 
 // out[t, h * dv + v] = heads[t * h_ts + h * h_hs + v] * sigmoid(gate[t * g_ts + h * dv + v])   (float32 arithmetic);
-// `heads` may be `out` itself laid out the same way (in place)
+// `heads` may be `out` itself laid out the same way (in place).  per_head: the gate is one number per head,
+// gate[t * g_ts + h]
 template <typename T>
 __global__ void gate_sigmoid_kernel(T* out, const T* heads, long long h_ts, long long h_hs,
-                                    const T* __restrict__ gate, long long g_ts, int nh, int dv, size_t n) {
+                                    const T* __restrict__ gate, long long g_ts, int nh, int dv, size_t n, int per_head) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const size_t w = (size_t)nh * dv;
     const size_t t = i / w, c = i % w;
     const int h = (int)(c / dv), v = (int)(c % dv);
-    const float g = to_f32<T>(gate[t * g_ts + c]);
+    const float g = to_f32<T>(gate[t * g_ts + (per_head ? (size_t)h : c)]);
     const float o = to_f32<T>(heads[t * h_ts + (size_t)h * h_hs + v]);
     out[i] = from_f32<T>(o / (1.f + expf(-g)));
 }
@@ -169,10 +170,10 @@ __global__ void gate_sigmoid_bf16x8_kernel(__nv_bfloat16* out, const __nv_bfloat
 }
 
 XB_EXPORT int xb_gate_sigmoid(int dtype, void* out, const void* heads, long long h_ts, long long h_hs, const void* gate,
-                              long long g_ts, int tokens, int nh, int dv, cudaStream_t stream) {
+                              long long g_ts, int tokens, int nh, int dv, int per_head, cudaStream_t stream) {
     const size_t n = (size_t)tokens * nh * dv;
     if (n == 0) return 0;
-    if (dtype == XB_BF16 && dv % 8 == 0 && h_ts % 8 == 0 && h_hs % 8 == 0 && g_ts % 8 == 0 &&
+    if (!per_head && dtype == XB_BF16 && dv % 8 == 0 && h_ts % 8 == 0 && h_hs % 8 == 0 && g_ts % 8 == 0 &&
         !(((uintptr_t)out | (uintptr_t)heads | (uintptr_t)gate) & 15)) {
         const int vecs = nh * dv / 8;
         const int threads = vecs >= 256 ? 256 : 64;
@@ -183,10 +184,10 @@ XB_EXPORT int xb_gate_sigmoid(int dtype, void* out, const void* heads, long long
     }
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == XB_F32)
-        gate_sigmoid_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, (const float*)heads, h_ts, h_hs, (const float*)gate, g_ts, nh, dv, n);
+        gate_sigmoid_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, (const float*)heads, h_ts, h_hs, (const float*)gate, g_ts, nh, dv, n, per_head);
     else
         gate_sigmoid_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)heads, h_ts, h_hs,
-                                                                      (const __nv_bfloat16*)gate, g_ts, nh, dv, n);
+                                                                      (const __nv_bfloat16*)gate, g_ts, nh, dv, n, per_head);
     return xb_launch_status();
 }
 

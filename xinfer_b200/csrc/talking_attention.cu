@@ -19,6 +19,10 @@
 //   rotation of the first `rot` channels by position * inv_freq[pair]  (inv_freq absent: none);
 //     cos and sin are multiplied by rot_mag (1: a pure rotation)
 //   norm_mode 2: x <- x / rms(x) * w
+//   norm_mode 3: like 1, but ONE root mean square over all of a token's q channels (and one over all of its k
+//     channels), with weights of heads x d (kv_heads x d) channels
+// The values are read at v_off of the row (the default lies behind q and k; the offset of k makes the keys as
+// projected, before norm and rotation, double as values; the bias is read at the same offset).
 // `bias` (float32, laid out like a qkv row; absent: none) is added to q, k and v first.  With temp_every > 0 a
 // query at position p is multiplied, last of all, by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1).
 // q goes to q_out[t, h], k and v into their pages ([page, kv_head, slot, d] and [.., dv]).
@@ -61,8 +65,9 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
                                    int table_stride, int nh, int nkv, int d, int dv, int rot, int interleaved, int norm_mode,
                                    int page_size, int num_pages, float eps, int write_kv, int vec4, float rot_mag,
                                    const float* __restrict__ bias, float temp_coef, int temp_every, long long row_len,
-                                   int* err) {
+                                   long long v_off, int* err) {
     extern __shared__ float sm[];
+    __shared__ float red[33];
     const int half = rot / 2;
     float* cs = sm;                 // [half]
     float* sn = sm + half;          // [half]
@@ -91,14 +96,24 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
         }
     }
     const T* row = qkv + (size_t)t * row_len;     // (a row may hold more behind its q, k and v)
+    float inv_q = 1.f, inv_k = 1.f;
+    if (norm_mode == 3) {     // one root mean square over the whole q projection, one over the whole k projection
+        float sq = 0.f, sk = 0.f;
+        for (int i = threadIdx.x; i < (nh + nkv) * d; i += blockDim.x) {
+            const float v = to_f32<T>(row[i]) + (bias ? bias[i] : 0.f);
+            if (i < nh * d) sq += v * v; else sk += v * v;
+        }
+        inv_q = 1.f / sqrtf(block_sum(sq, red) / (float)(nh * d) + eps);
+        inv_k = 1.f / sqrtf(block_sum(sk, red) / (float)(nkv * d) + eps);
+    }
     // the query's temperature: it grows with the logarithm of the number of whole periods the sequence has seen
     const float q_mul = temp_every > 0 ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f) : 1.f;
     for (int h = warp; h < nh + 2 * nkv; h += nwarps) {
         if (h >= nh + nkv) {      // a value head: copy (plus its bias)
             if (kv_row < 0) continue;
             const int g = h - nh - nkv;
-            const T* x = row + (size_t)(nh + nkv) * d + (size_t)g * dv;
-            const float* bv = bias ? bias + (size_t)(nh + nkv) * d + (size_t)g * dv : nullptr;
+            const T* x = row + v_off + (size_t)g * dv;
+            const float* bv = bias ? bias + v_off + (size_t)g * dv : nullptr;
             T* dst = v_cache + (size_t)(kv_row + (long long)g * page_size) * dv;
             if (vec4) {
                 for (int i = lane * 4; i < dv; i += 128) {
@@ -125,6 +140,7 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
         T* dst = is_q ? q_out + ((size_t)t * nh + h) * d
                       : k_cache + (size_t)(kv_row + (long long)(h - nh) * page_size) * d;
         const float* nw = is_q ? q_w : k_w;
+        if (norm_mode == 3 && nw) nw += (size_t)(is_q ? h : h - nh) * d;     // weights over the whole projection
         float ss = 0.f;
         if (vec4) {
             for (int i = lane * 4; i < d; i += 128) {
@@ -145,8 +161,8 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
             }
         }
         __syncwarp();
-        if (norm_mode == 1) {
-            const float inv = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
+        if (norm_mode == 1 || norm_mode == 3) {
+            const float inv = norm_mode == 3 ? (is_q ? inv_q : inv_k) : 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
             for (int i = lane; i < d; i += 32) xs[i] = xs[i] * inv * (nw ? nw[i] : 1.f);
             __syncwarp();
         }
@@ -185,9 +201,10 @@ XB_EXPORT int xb_qkv_prepare(int dtype, void* q_out, void* k_cache, void* v_cach
                              const float* k_w, const float* inv_freq, const int* positions, const int* req_of_token,
                              const int* block_table, int table_stride, int tokens, int nh, int nkv, int d, int dv, int rot,
                              int interleaved, int norm_mode, int page_size, int num_pages, float eps, int write_kv, float rot_mag,
-                             const float* bias, float temp_coef, int temp_every, long long row_len, int* err,
-                             cudaStream_t stream) {
+                             const float* bias, float temp_coef, int temp_every, long long row_len, long long v_off,
+                             int* err, cudaStream_t stream) {
     if (tokens <= 0) return 0;
+    if (v_off < 0) v_off = (long long)(nh + nkv) * d;
     // a warp per head at a time: as many warps as a token has heads, up to 16
     const int heads = nh + 2 * nkv;
     int threads = heads >= 16 ? 512 : (heads >= 8 ? 256 : 128);
@@ -199,18 +216,18 @@ XB_EXPORT int xb_qkv_prepare(int dtype, void* q_out, void* k_cache, void* v_cach
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     // four elements per access where every head starts on such a boundary, in the rows and in the pages
     const size_t esz = dtype == XB_F32 ? 4 : 2;
-    const int vec4 = (d % 4 == 0 && dv % 4 == 0 && row_len % 4 == 0 &&
+    const int vec4 = (d % 4 == 0 && dv % 4 == 0 && row_len % 4 == 0 && v_off % 4 == 0 &&
                       !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & (4 * esz - 1))) ? 1 : 0;
     if (dtype == XB_F32)
         qkv_prepare_kernel<float><<<tokens, threads, smem, stream>>>(
             (float*)q_out, (float*)k_cache, (float*)v_cache, (const float*)qkv, q_w, k_w, inv_freq, positions, req_of_token,
             block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode, page_size, num_pages, eps, write_kv, vec4, rot_mag,
-            bias, temp_coef, temp_every, row_len, err);
+            bias, temp_coef, temp_every, row_len, v_off, err);
     else
         qkv_prepare_kernel<__nv_bfloat16><<<tokens, threads, smem, stream>>>(
             (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const __nv_bfloat16*)qkv, q_w, k_w,
             inv_freq, positions, req_of_token, block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode,
-            page_size, num_pages, eps, write_kv, vec4, rot_mag, bias, temp_coef, temp_every, row_len, err);
+            page_size, num_pages, eps, write_kv, vec4, rot_mag, bias, temp_coef, temp_every, row_len, v_off, err);
     return xb_launch_status();
 }
 

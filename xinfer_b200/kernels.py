@@ -310,12 +310,15 @@ def qk_norm_rope_write(q_out, k_cache, v_cache, qkv, q_w, k_w, cos_t, sin_t, pos
 
 
 def attention_plain(out, q, k_cache, v_cache, positions, req_of_token, block_table, table_stride, window, scale, err, *,
-                    sink=None, value_dim=None):
+                    sink=None, value_dim=None, softcap=None, slope_exponent=None, chunk=None):
     """Attention of every token over its request's cached positions, one warp per (token, head), float32 scores,
     softmax and value sums.  ``q`` is ``[T, heads, d]``, ``out`` ``[T, heads, dv]``.  The caches are
     ``[page, kv_head, slot, d]`` and ``[page, kv_head, slot, dv]``; with ``value_dim`` the values are the first
     ``value_dim`` channels of the key rows themselves (``v_cache`` is then ignored).  ``sink`` (float32 per head):
-    one more softmax entry of that score without a value."""
+    one more softmax entry of that score without a value.  ``softcap``: scores pass ``cap * tanh(s / cap)``;
+    ``slope_exponent`` x: head h's score of a key ``dist`` positions back loses ``2^(-x (h + 1) / heads) * dist``
+    (after the cap); ``chunk``: a query sees the keys of its own chunk of that many positions, counted from the
+    sequence's start, instead of a window."""
     T, nh, d = q.shape
     _need(q, "q", None, (T, nh, d))
     _need(k_cache, "k_cache", q.dtype, (None, None, None, d))
@@ -339,25 +342,41 @@ def attention_plain(out, q, k_cache, v_cache, positions, req_of_token, block_tab
     _ok(kernels_lib().xb_attention_plain(
         dtype_code(q.dtype), out.data_ptr(), q.data_ptr(), nh * d, d, k_cache.data_ptr(), v_cache.data_ptr(), d, v_stride,
         _ptr(sink), positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), int(table_stride), T, nh, nkv, d,
-        dv, page_size, num_pages, int(window or 0), float(scale), err.data_ptr(), _stream()), "attention_plain")
+        dv, page_size, num_pages, int(window or 0), float(scale), float(softcap or 0.0), float(slope_exponent or 0.0),
+        int(chunk or 0), err.data_ptr(), _stream()), "attention_plain")
 
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+# activations of a gated feed-forward by code.  "swish_clamp" takes two parameters (limit, alpha): with
+# a = min(gate, limit) and b = clamp(up, -limit, limit) the product is a * sigmoid(alpha * a) * (b + 1).
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu": 2, "swish_clamp": 3}
 
 
-def swiglu(out, gate_up, activation: str = "silu"):
-    """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i]; ``activation``: "silu" or "gelu_tanh"."""
-    act = ACTIVATIONS[activation]
+def activation_args(activation: str, params=()) -> tuple:
+    """(code, p0, p1) of an activation and its parameters for the kernels."""
+    code = ACTIVATIONS[activation]
+    params = tuple(float(p) for p in (params or ()))
+    if activation == "swish_clamp":
+        if len(params) != 2 or not params[0] > 0:
+            raise KernelError(f"'swish_clamp' takes (limit > 0, alpha), got {params}")
+        return code, params[0], params[1]
+    if params:
+        raise KernelError(f"the activation '{activation}' takes no parameters")
+    return code, 0.0, 0.0
+
+
+def swiglu(out, gate_up, activation: str = "silu", params=()):
+    """out[t, i] = act(gate_up[t, i]) * f(gate_up[t, I + i]); ``activation``: a key of ``ACTIVATIONS``."""
+    act, p0, p1 = activation_args(activation, params)
     T, two_i = gate_up.shape
     _need(gate_up, "gate_up", None, (T, two_i))
     _need(out, "out", gate_up.dtype, (T, two_i // 2))
     if vectorized and gate_up.dtype == torch.bfloat16 and two_i % 16 == 0:
         if T >= many_rows:
-            _ok(kernels_lib().xb_swiglu_rows_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, act, _stream()), "swiglu_rows_bf16")
+            _ok(kernels_lib().xb_swiglu_rows_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, act, p0, p1, _stream()), "swiglu_rows_bf16")
             return
-        _ok(kernels_lib().xb_swiglu_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, act, _stream()), "swiglu_bf16")
+        _ok(kernels_lib().xb_swiglu_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, act, p0, p1, _stream()), "swiglu_bf16")
         return
-    _ok(kernels_lib().xb_swiglu(dtype_code(gate_up.dtype), out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, act, _stream()), "swiglu")
+    _ok(kernels_lib().xb_swiglu(dtype_code(gate_up.dtype), out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, act, p0, p1, _stream()), "swiglu")
 
 
 def widen_bf16(out, x):
@@ -669,20 +688,24 @@ def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, block_table, t
 # ---- attention with talking heads and a sink; gated recurrence; polynomial activation; table experts ----
 def qkv_prepare(q_out, k_cache, v_cache, qkv, q_w, k_w, inv_freq, positions, req_of_token, block_table, table_stride,
                 nh, nkv, d, dv, rot, interleaved, norm_mode, eps, write_kv, err, rot_magnitude: float = 1.0, bias=None,
-                q_temp=None, row_len=None):
+                q_temp=None, row_len=None, value_offset=None):
     """Per q/k head of the packed ``qkv`` rows ``[heads*d | kv_heads*d | kv_heads*dv]``: norm over the head
     (``norm_mode`` 1: before the rotation, 2: after it, 0: none; weight ``q_w`` / ``k_w`` or none), rotation of
     the first ``rot`` channels by ``position * inv_freq`` (float32 angles formed in the kernel; ``inv_freq`` None:
     no rotation; cos and sin are multiplied by ``rot_magnitude``); q to ``q_out``, k and v into their pages.
     ``bias`` (float32, as long as a ``qkv`` row) is added first of all.  ``q_temp`` = (coef, every): a query at
-    position p is multiplied, last of all, by ``1 + coef * ln(floor((p + 1) / every) + 1)``."""
+    position p is multiplied, last of all, by ``1 + coef * ln(floor((p + 1) / every) + 1)``.  ``norm_mode`` 3: like 1
+    with ONE root mean square over all q channels of a token (and one over all its k channels) and weights of
+    ``heads * d`` (``kv_heads * d``) channels.  ``value_offset``: where in a row the values start (default: behind q
+    and k); the offset of k makes the keys as projected double as values, and rows then hold no values of their own."""
     T = qkv.shape[0]
-    need_len = (nh + nkv) * d + nkv * dv
+    v_off = (nh + nkv) * d if value_offset is None else int(value_offset)
+    need_len = max((nh + nkv) * d, v_off + nkv * dv)
     row_len = need_len if row_len is None else int(row_len)     # rows may hold more behind their q, k and v
     if row_len < need_len:
         raise KernelError(f"rows of {row_len} elements cannot hold q, k and v of {need_len}")
     if bias is not None:
-        _need(bias, "bias", torch.float32, ((nh + nkv) * d + nkv * dv,))
+        _need(bias, "bias", torch.float32, (need_len,))
     coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp is not None else (0.0, 0)
     if q_temp is not None and every <= 0:
         raise KernelError(f"the query temperature's period must be positive, got {every}")
@@ -693,17 +716,17 @@ def qkv_prepare(q_out, k_cache, v_cache, qkv, q_w, k_w, inv_freq, positions, req
         _need(v_cache, "v_cache", qkv.dtype, (k_cache.shape[0], nkv, k_cache.shape[2], dv))
     num_pages = k_cache.shape[0] if k_cache is not None else 0
     page_size = k_cache.shape[2] if k_cache is not None else 1
-    for name, w_ in (("q_norm", q_w), ("k_norm", k_w)):
+    for name, w_, n_ in (("q_norm", q_w, nh), ("k_norm", k_w, nkv)):
         if w_ is not None:
-            _need(w_, name, torch.float32, (d,))
+            _need(w_, name, torch.float32, (n_ * d if norm_mode == 3 else d,))
     if inv_freq is not None:
         _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
     _ok(kernels_lib().xb_qkv_prepare(
         dtype_code(qkv.dtype), q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache), qkv.data_ptr(), _ptr(q_w), _ptr(k_w),
         _ptr(inv_freq), positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), int(table_stride), T, nh, nkv,
         d, dv, int(rot if inv_freq is not None else 0), int(bool(interleaved)), int(norm_mode), page_size, num_pages,
-        float(eps), int(bool(write_kv)), float(rot_magnitude), _ptr(bias), coef, every, row_len, err.data_ptr(), _stream()),
-        "qkv_prepare")
+        float(eps), int(bool(write_kv)), float(rot_magnitude), _ptr(bias), coef, every, row_len, v_off, err.data_ptr(),
+        _stream()), "qkv_prepare")
 
 
 def attn_talking_tile(nh: int, d: int, dv: int, want: int) -> int:
@@ -810,12 +833,14 @@ def polynorm(out, z, coef, eps):
 
 
 def expert_route(offsets, perm, inv, table, ids, sampled, req_of_token, tokens, top, experts, err):
+    """Groups the step's (token, choice) pairs by expert.  The experts of token t are ``table[ids[t]]``, or
+    ``table[t]`` where ``ids`` is None (the table then holds a router's choices for the step's tokens)."""
     _need(table, "table", torch.int32, (None, top))
     for name, t_, n in (("offsets", offsets, experts + 1), ("perm", perm, tokens * top), ("inv", inv, tokens * top)):
         _need(t_, name, torch.int32)
         if t_.numel() < n:
             raise KernelError(f"{name} holds {t_.numel()} entries, {n} are needed")
-    _ok(kernels_lib().xb_expert_route(offsets.data_ptr(), perm.data_ptr(), inv.data_ptr(), table.data_ptr(), ids.data_ptr(),
+    _ok(kernels_lib().xb_expert_route(offsets.data_ptr(), perm.data_ptr(), inv.data_ptr(), table.data_ptr(), _ptr(ids),
                                       _ptr(sampled), sampled.numel() if sampled is not None else 0, req_of_token.data_ptr(),
                                       int(tokens), int(top), int(experts), table.shape[0], err.data_ptr(), _stream()),
         "expert_route")
@@ -825,9 +850,10 @@ def expert_route(offsets, perm, inv, table, ids, sampled, req_of_token, tokens, 
 expert_tensor_cores = True
 
 
-def expert_gemm(y, a, w, offsets, perm, gather: bool, top: int, gated: bool, *, side_by_side: bool = False):
+def expert_gemm(y, a, w, offsets, perm, gather: bool, top: int, gated: bool, *, side_by_side: bool = False,
+                activation: str = "silu", params=()):
     """y[r] = a[src(r)] . w[e(r)]^T over rows grouped by expert (``expert_route``).  ``w`` is
-    ``[experts, N, K]`` (``[experts, 2 N, K]`` when ``gated``: y = silu(gate) * up), or with
+    ``[experts, N, K]`` (``[experts, 2 N, K]`` when ``gated``: y = act(gate) * f(up), ``activation``), or with
     ``side_by_side`` ``[N, experts * K]``: the experts' matrices beside each other along K."""
     rows = y.shape[0]
     if side_by_side:
@@ -843,31 +869,38 @@ def expert_gemm(y, a, w, offsets, perm, gather: bool, top: int, gated: bool, *, 
         ldw, estride = K, w.shape[1] * K
     _need(a, "a", None, (None, K))
     _need(y, "y", None, (rows, N))
+    act, p0, p1 = activation_args(activation, params)
     if expert_tensor_cores and a.dtype == torch.bfloat16 and K % 8 == 0:
         rc = kernels_lib().xb_expert_gemm_mma(dtype_code(y.dtype), y.data_ptr(), a.data_ptr(), w.data_ptr(), offsets.data_ptr(),
                                               perm.data_ptr(), int(bool(gather)), int(top), E, rows, N, K, int(bool(gated)),
-                                              ldw, estride, _stream())
+                                              ldw, estride, act, p0, p1, _stream())
         if rc != ERR_NOT_SUPPORTED:
             _ok(rc, "expert_gemm_mma")
             return
     _ok(kernels_lib().xb_expert_gemm(dtype_code(a.dtype), dtype_code(y.dtype), y.data_ptr(), a.data_ptr(), w.data_ptr(),
                                      offsets.data_ptr(), perm.data_ptr(), int(bool(gather)), int(top), E, rows, N, K,
-                                     int(bool(gated)), ldw, estride, _stream()), "expert_gemm")
+                                     int(bool(gated)), ldw, estride, act, p0, p1, _stream()), "expert_gemm")
 
 
-def expert_select_gate(act, gu, table, ids, sampled, req_of_token, top: int, experts: int, err):
+def expert_select_gate(act, gu, table, ids, sampled, req_of_token, top: int, experts: int, err, *, weights=None,
+                       activation: str = "silu", params=()):
     """From every expert's gate/up values of every token, ``gu [T, experts * 2 F]``, the inputs of the down
     product with the experts side by side: ``act [T, experts * F]`` holds ``silu(gate) * up / top`` for a
-    token's own experts and zero for the others."""
+    token's own experts and zero for the others.  ``ids`` None: ``table`` has a row per token of the step;
+    ``weights`` (float32, like ``table``): a chosen expert's own weight instead of 1 / top; ``activation`` as in
+    ``swiglu``."""
     T = gu.shape[0]
+    code, p0, p1 = activation_args(activation, params)
+    if weights is not None:
+        _need(weights, "weights", torch.float32, tuple(table.shape))
     Fdim = gu.shape[1] // (2 * experts)
     _need(gu, "gu", None, (T, experts * 2 * Fdim))
     _need(act, "act", gu.dtype, (T, experts * Fdim))
     _need(table, "table", torch.int32, (None, top))
-    _ok(kernels_lib().xb_expert_select_gate(dtype_code(gu.dtype), act.data_ptr(), gu.data_ptr(), table.data_ptr(), ids.data_ptr(),
+    _ok(kernels_lib().xb_expert_select_gate(dtype_code(gu.dtype), act.data_ptr(), gu.data_ptr(), table.data_ptr(), _ptr(ids),
                                             _ptr(sampled), sampled.numel() if sampled is not None else 0,
                                             req_of_token.data_ptr(), T, int(top), int(experts), Fdim, table.shape[0],
-                                            err.data_ptr(), _stream()), "expert_select_gate")
+                                            _ptr(weights), code, p0, p1, err.data_ptr(), _stream()), "expert_select_gate")
 
 
 def expert_gather(out, x, perm, offsets, top: int):
@@ -879,12 +912,38 @@ def expert_gather(out, x, perm, offsets, top: int):
                                        rows, int(top), offsets.numel() - 1, K, _stream()), "expert_gather")
 
 
-def expert_combine(out, y, inv, top: int):
+def expert_combine(out, y, inv, top: int, *, weights=None, base=None):
+    """out[t] = base[t] + sum_k w(t, k) y[inv[t, k]]: a token's experts summed in the order of k, each times its own
+    weight (``weights`` float32 ``[T, top]``) or all times 1 / top; ``base`` (like ``out``, may be ``out``) is added."""
     T, N = out.shape
     _need(y, "y", torch.float32, (None, N))
     _need(out, "out", None, (T, N))
+    if weights is not None:
+        _need(weights, "weights", torch.float32, (T, top))
+    if base is not None:
+        _need(base, "base", out.dtype, (T, N))
     _ok(kernels_lib().xb_expert_combine(dtype_code(out.dtype), out.data_ptr(), y.data_ptr(), inv.data_ptr(), T, int(top), N,
-                                        _stream()), "expert_combine")
+                                        _ptr(weights), _ptr(base), _stream()), "expert_combine")
+
+
+def expert_router(choice, weight, h, w_router, correction, req_of_token, top: int, groups: int = 1, keep: int = 1,
+                  group_best: int = 2, renormalize: bool = False):
+    """A sigmoid router: scores ``s = sigmoid(W_r h)`` in float32, choice scores ``s + correction``; only experts of
+    the ``keep`` best of ``groups`` equal groups of neighbours can be chosen (a group's score: the sum of its
+    ``group_best`` largest choice scores); ``choice [T, top]`` (int32) receives the experts with the largest choice
+    scores and ``weight [T, top]`` their plain scores (divided by their sum with ``renormalize``)."""
+    T, K = h.shape
+    E = w_router.shape[0]
+    _need(h, "h", None, (T, K))
+    _need(w_router, "w_router", torch.float32, (E, K))
+    _need(choice, "choice", torch.int32, (T, top))
+    _need(weight, "weight", torch.float32, (T, top))
+    if correction is not None:
+        _need(correction, "correction", torch.float32, (E,))
+    _ok(kernels_lib().xb_expert_router(dtype_code(h.dtype), choice.data_ptr(), weight.data_ptr(), h.data_ptr(),
+                                       w_router.data_ptr(), _ptr(correction), req_of_token.data_ptr(), T, E, K, int(top),
+                                       int(groups), int(keep), int(group_best), int(bool(renormalize)), _stream()),
+        "expert_router")
 
 
 # ---- attention over a cached latent ---------------------------------------------------------------------------------
@@ -951,15 +1010,16 @@ def attn_latent_mma(out, q, cache, q_start, start_pos, num_entries, block_table,
 def gate_sigmoid(out, heads, gate):
     """out[t, h, :] = heads[h, t, :] * sigmoid(gate[t, h, :]).  ``heads`` ``[heads, T, dv]`` may be any view with a
     unit last stride - also ``out`` itself seen head by head (in place); ``gate`` may be a column range of a wider
-    tensor."""
+    tensor.  A gate of ``[T, heads]`` is one number per head."""
     nh, T, dv = heads.shape
     if not heads.is_cuda or heads.stride(2) != 1:
         raise KernelError("heads must be a CUDA view [heads, T, dv] with a unit last stride")
     _need(out, "out", heads.dtype, (T, nh * dv))
-    if (gate.dtype != heads.dtype or tuple(gate.shape) != (T, nh * dv) or gate.stride(1) != 1 or not gate.is_cuda):
-        raise KernelError("gate must be a [T, heads * dv] view with unit column stride in the heads' type")
+    per_head = dv != 1 and tuple(gate.shape) == (T, nh)
+    if (gate.dtype != heads.dtype or tuple(gate.shape) not in ((T, nh * dv), (T, nh)) or gate.stride(1) != 1 or not gate.is_cuda):
+        raise KernelError("gate must be a [T, heads * dv] or [T, heads] view with unit column stride in the heads' type")
     _ok(kernels_lib().xb_gate_sigmoid(dtype_code(heads.dtype), out.data_ptr(), heads.data_ptr(), heads.stride(1), heads.stride(0),
-                                      gate.data_ptr(), gate.stride(0), T, nh, dv, _stream()), "gate_sigmoid")
+                                      gate.data_ptr(), gate.stride(0), T, nh, dv, int(per_head), _stream()), "gate_sigmoid")
 
 
 def gemm_batched_plain(out, a, w):
@@ -1040,6 +1100,8 @@ def swiglu_bias(out, gate_up, bias, activation: str = "silu"):
     _need(gate_up, "gate_up", None, (T, two_i))
     _need(out, "out", None, (T, two_i // 2))
     _need(bias, "bias", torch.float32, (two_i,))
+    if activation not in ("silu", "gelu_tanh"):
+        raise KernelError(f"the gate with biases takes silu or gelu_tanh, not '{activation}'")
     _ok(kernels_lib().xb_swiglu_bias(dtype_code(gate_up.dtype), dtype_code(out.dtype), out.data_ptr(), gate_up.data_ptr(),
                                      bias.data_ptr(), T, two_i // 2, ACTIVATIONS[activation], _stream()), "swiglu_bias")
 

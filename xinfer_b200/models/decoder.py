@@ -1,6 +1,7 @@
 """The generic decoder: builds any ``ModelPlan`` from registered parts and runs one step of it.
 
-embedding (times the plan's ``embed_scale``, if it has one) -> the plan's layer runs in order ->
+embedding (times the plan's ``embed_scale``, if it has one) -> the plan's layer runs in order (a run may add the
+embedding's output to the stream again: layers that are run several times in a row start every pass but the first so) ->
 final norm on the wanted rows -> output head -> the plan's logit scale and soft cap, if any.
 (The reference's forward for this architecture: src/models/qwen3.rs:311-374.)
 """
@@ -14,7 +15,7 @@ import torch
 from .. import kernels, tracing
 from ..config.plan import ModelPlan
 from ..parts import Block, LayerCache, StepContext, build_part, part_class
-from ..parts.block import Stream, fused_norm
+from ..parts.block import Addend, Stream, fused_norm
 from ..parts.linear import linear
 from ..weights.loader import WeightSpec, WeightStore
 
@@ -155,7 +156,14 @@ class DecoderModel:
         if trace:
             tracing.pop()
         stream = Stream(x)
+        x0 = None
+        if any(run.add_input for run in self.plan.runs):
+            # runs that add the embedding's output again: it is kept apart from the stream that the blocks change
+            x0 = ws.get("model.x0", (T, H), self.stream_dtype)
+            x0.copy_(x)
         for pos, run in enumerate(self.plan.runs):
+            if run.add_input:
+                stream.pending.append(Addend(x0))      # summed by whoever reads the stream next
             src = pos if run.cache_from is None else run.cache_from
             stream = self.blocks[run.block].forward(stream, ctx, caches[src], states[pos],
                                                     writes_cache=run.cache_from is None)

@@ -93,17 +93,17 @@ def _declare_kernels(lib):
     _sig(lib, "xb_rope_table", I, [P, P, P, I, I, P])
     _sig(lib, "xb_qk_norm_rope_write", I,
          [I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P])
-    _sig(lib, "xb_attention_plain", I, [I, P, P, L, L, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P])
-    _sig(lib, "xb_swiglu", I, [I, P, P, I, I, I, P])
+    _sig(lib, "xb_attention_plain", I, [I, P, P, L, L, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, F, I, P, P])
+    _sig(lib, "xb_swiglu", I, [I, P, P, I, I, I, F, F, P])
     _sig(lib, "xb_widen_bf16", I, [P, P, L, P])
     _sig(lib, "xb_sample", I, [P, P, P, P, I, I, I, I, P, P, P])
     _sig(lib, "xb_sample_scratch_bytes", c_longlong, [I])
     _sig(lib, "xb_sample_params_size", I, [])
     _sig(lib, "xb_rmsnorm_bf16", I, [P, P, P, P, P, P, I, I, I, F, F, P, P])
-    _sig(lib, "xb_swiglu_bf16", I, [P, P, I, I, I, P])
+    _sig(lib, "xb_swiglu_bf16", I, [P, P, I, I, I, F, F, P])
     _sig(lib, "xb_qk_norm_rope_write_bf16", I,
          [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P])
-    _sig(lib, "xb_swiglu_rows_bf16", I, [P, P, I, I, I, P])
+    _sig(lib, "xb_swiglu_rows_bf16", I, [P, P, I, I, I, F, F, P])
     _sig(lib, "xb_attn_prefill_tc", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P])
     _sig(lib, "xb_gemm_skinny_tc", I, [P, I, P, P, I, I, I, I, P, P])
     _sig(lib, "xb_gemm_skinny_swiglu", I, [P, P, P, I, I, I, I, P, P])
@@ -117,7 +117,7 @@ def _declare_kernels(lib):
     _sig(lib, "xb_embedding_f32", I, [I, P, P, P, P, I, I, I, I, F, P, P])
     _sig(lib, "xb_rmsnorm_f32", I, [I, I, P, P, P, P, P, P, I, I, I, F, F, P, P])
     _sig(lib, "xb_add_f32", I, [I, P, P, P, L, F, P])
-    _sig(lib, "xb_qkv_prepare", I, [I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, F, P, F, I, L, P, P])
+    _sig(lib, "xb_qkv_prepare", I, [I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, F, P, F, I, L, L, P, P])
     _sig(lib, "xb_rms_chain", I, [I, I, P, P, P, P, P, P, P, P, I, I, I, F, F, F, F, F, P, P])
     _sig(lib, "xb_dual_rms_sum", I, [I, P, P, P, P, P, I, I, F, F, F, F, P])
     _sig(lib, "xb_add_bias", I, [I, P, P, I, I, P])
@@ -134,7 +134,7 @@ def _declare_kernels(lib):
     _sig(lib, "xb_latent_prepare", I, [I, P, P, P, L, I, I, P, L, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, P, P])
     _sig(lib, "xb_attn_latent_mma_takes", I, [I, I])
     _sig(lib, "xb_attn_latent_mma", I, [P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, I, I, P, P, P, P])
-    _sig(lib, "xb_gate_sigmoid", I, [I, P, P, L, L, P, L, I, I, I, P])
+    _sig(lib, "xb_gate_sigmoid", I, [I, P, P, L, L, P, L, I, I, I, I, P])
     _sig(lib, "xb_gemm_batched_plain", I, [I, P, P, P, I, I, I, I, L, L, L, L, L, L, L, P])
     _sig(lib, "xb_attn_talking_tile", I, [I, I, I, I])
     _sig(lib, "xb_attn_talking", I, [I, P, I, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, I, F, I, I, P, P, P, P])
@@ -143,9 +143,10 @@ def _declare_kernels(lib):
     _sig(lib, "xb_gated_scan", I, [I, P, I, P, P, P, P, P, P, P, I, I, I, F, I, P, P])
     _sig(lib, "xb_polynorm", I, [I, P, P, P, I, I, F, P])
     _sig(lib, "xb_expert_route", I, [P, P, P, P, P, P, I, P, I, I, I, I, P, P])
-    _sig(lib, "xb_expert_gemm", I, [I, I, P, P, P, P, P, I, I, I, I, I, I, I, L, L, P])
-    _sig(lib, "xb_expert_select_gate", I, [I, P, P, P, P, P, I, P, I, I, I, I, I, P, P])
-    _sig(lib, "xb_expert_gemm_mma", I, [I, P, P, P, P, P, I, I, I, I, I, I, I, L, L, P])
+    _sig(lib, "xb_expert_gemm", I, [I, I, P, P, P, P, P, I, I, I, I, I, I, I, L, L, I, F, F, P])
+    _sig(lib, "xb_expert_select_gate", I, [I, P, P, P, P, P, I, P, I, I, I, I, I, P, I, F, F, P, P])
+    _sig(lib, "xb_expert_gemm_mma", I, [I, P, P, P, P, P, I, I, I, I, I, I, I, L, L, I, F, F, P])
     _sig(lib, "xb_expert_gather", I, [I, P, P, P, P, I, I, I, I, P])
-    _sig(lib, "xb_expert_combine", I, [I, P, P, P, I, I, I, P])
+    _sig(lib, "xb_expert_combine", I, [I, P, P, P, I, I, I, P, P, P])
+    _sig(lib, "xb_expert_router", I, [I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P])
     _sig(lib, "xb_attn_decode_tc", I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, I, P, P])

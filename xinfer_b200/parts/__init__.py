@@ -3,7 +3,7 @@ from .base import (CacheTensor, FeedForward, LayerCache, Mixer, Norm, PagedCache
                    StepContext, Workspace, build_part, part_class, register_feed_forward,
                    register_mixer, register_norm, register_position_encoding, unregister)
 from . import (norm, rope, attention, swiglu, talking_attention, min_gru, parallel, polynorm_mlp,  # noqa: F401
-               table_experts, latent_attention, selective_state, gated_delta, token_side)                                                           # (register the built-in kinds)
+               table_experts, latent_attention, selective_state, gated_delta, token_side, routed_experts)                                                           # (register the built-in kinds)
 from .block import Block
 
 __all__ = [

@@ -7,6 +7,13 @@
     p_h[i, j]   = exp(s_h[i, j]) / (sink + sum_j' exp(s_h[i, j']))      sink = 1 (``sink``) or 0
     out         = W_o concat_h( sum_j p_h[i, j] v_kv(h)[j] )
 
+Options of the spec beyond that: biases on q, k, v (and the output projection); keys that double as values
+(``value_from_key``: v is the k projection with its bias, before norm and rotation, and there is no W_v); ONE norm
+over the whole q (k) projection instead of one per head; a cap on the scores, ``cap * tanh(s / cap)``; a bias on
+the distance after the cap, ``- 2^(-x (h + 1) / heads) * (i - j)``; a chunked mask (a query sees the earlier keys
+of its own chunk of positions, counted from the sequence's start); a sigmoid gate on the heads' outputs, one number
+per channel or per head.
+
 Causal, optionally within a window; query head h reads key/value head h // (heads / kv_heads).  With a
 sink the weights of a row sum to less than one: a query may attend to nothing.  Keys after rotation and
 norm, and values, live in the paged cache; scores, mix, softmax and value sums are float32.
@@ -48,7 +55,14 @@ class TalkingAttention(Mixer):
         if self.position is not None and not hasattr(self.position, "frequencies"):
             raise ValueError("this attention needs a rotary position encoding that offers its frequencies")
         self.names = tuple(spec.names) if spec.names else _DEFAULT_NAMES
-        self.w_qkv = self.w_o = self.talk = self.q_norm = self.k_norm = self.bias = None
+        self.w_qkv = self.w_o = self.talk = self.q_norm = self.k_norm = self.bias = self.b_o = None
+        if spec.value_from_key and spec.value_dim != spec.head_dim:
+            raise ValueError(f"keys of {spec.head_dim} channels cannot double as values of {spec.value_dim}")
+        if spec.chunk is not None and spec.window is not None:
+            raise ValueError("an attention takes a window or a chunked mask, not both")
+        if (spec.score_softcap is not None or spec.distance_slope_exponent is not None or spec.chunk is not None) and (
+                spec.talking_heads or spec.sink):
+            raise ValueError("a score cap, a distance bias and a chunked mask are not built for talking heads or a sink")
 
     @classmethod
     def weight_specs(cls, spec: AttentionSpec, prefix: str) -> List[WeightSpec]:
@@ -57,32 +71,40 @@ class TalkingAttention(Mixer):
         out = [
             WeightSpec(prefix + n[0], (spec.num_heads * d, spec.hidden)),
             WeightSpec(prefix + n[1], (spec.num_kv_heads * d, spec.hidden)),
-            WeightSpec(prefix + n[2], (spec.num_kv_heads * dv, spec.hidden)),
-            WeightSpec(prefix + n[3], (spec.hidden, spec.num_heads * dv)),
         ]
+        if not spec.value_from_key:
+            out.append(WeightSpec(prefix + n[2], (spec.num_kv_heads * dv, spec.hidden)))
+        out.append(WeightSpec(prefix + n[3], (spec.hidden, spec.num_heads * dv)))
         if spec.talking_heads:
             out.append(WeightSpec(prefix + n[4], (spec.num_heads, spec.num_heads), "unit"))
         if spec.qk_norm and spec.qk_norm_weight:
             qn, kn = spec.qk_norm_names or _DEFAULT_NORM_NAMES
-            out += [WeightSpec(prefix + qn, (d,), "norm"), WeightSpec(prefix + kn, (d,), "norm")]
+            nq, nk = (spec.num_heads * d, spec.num_kv_heads * d) if spec.qk_norm_whole else (d, d)
+            out += [WeightSpec(prefix + qn, (nq,), "norm"), WeightSpec(prefix + kn, (nk,), "norm")]
         if spec.bias_suffix:
             out += [WeightSpec(prefix + n[0] + spec.bias_suffix, (spec.num_heads * d,), "around_zero"),
-                    WeightSpec(prefix + n[1] + spec.bias_suffix, (spec.num_kv_heads * d,), "around_zero"),
-                    WeightSpec(prefix + n[2] + spec.bias_suffix, (spec.num_kv_heads * dv,), "around_zero")]
+                    WeightSpec(prefix + n[1] + spec.bias_suffix, (spec.num_kv_heads * d,), "around_zero")]
+            if not spec.value_from_key:
+                out.append(WeightSpec(prefix + n[2] + spec.bias_suffix, (spec.num_kv_heads * dv,), "around_zero"))
+            if spec.out_bias:
+                out.append(WeightSpec(prefix + n[3] + spec.bias_suffix, (spec.hidden,), "around_zero"))
         if spec.gate_name:
-            out.append(WeightSpec(prefix + spec.gate_name, (spec.num_heads * dv, spec.hidden)))
+            out.append(WeightSpec(prefix + spec.gate_name, (spec.num_heads * (1 if spec.gate_per_head else dv), spec.hidden)))
         return out
 
     def load(self, store) -> None:
         p, n, s = self.prefix, self.names, self.spec
-        parts = [store.get(p + n[i], self.device, self.dtype, operand=True) for i in range(3)]
+        own = (0, 1) if s.value_from_key else (0, 1, 2)      # keys that double as values: the row is [q | k (| gate)]
+        parts = [store.get(p + n[i], self.device, self.dtype, operand=True) for i in own]
         if s.gate_name:     # the gate reads the same input: one product gives [q | k | v | gate]
             parts.append(store.get(p + s.gate_name, self.device, self.dtype, operand=True))
         self.w_qkv = torch.cat(parts, dim=0).contiguous()
         del parts
         if s.bias_suffix:
             self.bias = torch.cat([store.get(p + n[i] + s.bias_suffix, self.device, torch.float32).float()
-                                   for i in range(3)]).contiguous()
+                                   for i in own]).contiguous()
+            if s.out_bias:
+                self.b_o = store.get(p + n[3] + s.bias_suffix, self.device, torch.float32).float().contiguous()
         self.w_o = store.get(p + n[3], self.device, self.dtype, operand=True)
         if s.talking_heads:
             self.talk = store.get(p + n[4], self.device, torch.float32).float().contiguous()
@@ -101,7 +123,13 @@ class TalkingAttention(Mixer):
         ordinary grouped-query one, and the engine's tcgen05 kernels (work lists, decode plans) take it."""
         s = self.spec
         return (USE_ATTENTION_BACKEND and not s.talking_heads and not s.sink and s.value_dim == s.head_dim
+                and not self._changed_scores()
                 and self.dtype == torch.bfloat16 and kernels.attn_tiled_supported(self.dtype, s.head_dim))
+
+    def _changed_scores(self) -> bool:
+        """A cap, a distance bias or a chunked mask: what the ordinary attention kernels do not know."""
+        s = self.spec
+        return s.score_softcap is not None or s.distance_slope_exponent is not None or s.chunk is not None
 
     def prepare_step(self, ctx: StepContext, cache: LayerCache) -> None:
         if self._plain_softmax():
@@ -122,9 +150,9 @@ class TalkingAttention(Mixer):
         T = x.shape[0]
         nh, nkv, d, dv = s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim
         ws = ctx.workspace
-        nqkv = (nh + nkv) * d + nkv * dv
+        nqkv = (nh + nkv) * d + (0 if s.value_from_key else nkv * dv)
         if s.gate_name:
-            proj = ws.get("tattn.qkvg", (T, nqkv + nh * dv), self.dtype)
+            proj = ws.get("tattn.qkvg", (T, nqkv + nh * (1 if s.gate_per_head else dv)), self.dtype)
             linear(proj, x, self.w_qkv, ctx.err)
             qkv = proj
         else:
@@ -133,13 +161,13 @@ class TalkingAttention(Mixer):
         q = ws.get("tattn.q", (T, nh, d), self.dtype)
         table, stride = ctx.tables[cache.group], ctx.strides[cache.group]
         rope = self.position.spec if self.position is not None else None
-        norm_mode = 0 if not s.qk_norm else (2 if s.qk_norm_after_rope else 1)
+        norm_mode = 0 if not s.qk_norm else (2 if s.qk_norm_after_rope else (3 if s.qk_norm_whole else 1))
         kernels.qkv_prepare(q, cache["k"], cache["v"], qkv, self.q_norm, self.k_norm,
                             self.position.frequencies() if rope is not None else None, ctx.positions, ctx.req_of_token,
                             table, stride, nh, nkv, d, dv, rope.rotary_dim if rope is not None else 0,
                             rope is not None and rope.layout == "interleaved", norm_mode, s.qk_norm_eps, writes_cache,
                             ctx.err, rot_magnitude=rope.magnitude if rope is not None else 1.0, bias=self.bias,
-                            q_temp=s.q_temp, row_len=qkv.shape[1])
+                            q_temp=s.q_temp, row_len=qkv.shape[1], value_offset=nh * d if s.value_from_key else None)
         self._attend(q, ctx, cache, table, stride, out, out_scale)
         if s.gate_name:
             kernels.gate_sigmoid(out, out.view(T, nh, dv).transpose(0, 1), qkv[:, nqkv:])
@@ -160,6 +188,13 @@ class TalkingAttention(Mixer):
         mma = (USE_TENSOR_CORES and self.dtype == torch.bfloat16 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
                and kernels.attn_talking_mma_tile(nh, nkv, d, dv, longest) > 0)
         bq = kernels.attn_talking_mma_tile(nh, nkv, d, dv, longest) if mma else kernels.attn_talking_tile(nh, d, dv, longest)
+        if self._changed_scores():
+            if out_scale != 1.0 or not out.is_contiguous():
+                raise kernels.KernelError("attention with changed scores writes a contiguous, unscaled result")
+            kernels.attention_plain(out.view(T, nh, dv), q, cache["k"], cache["v"], ctx.positions, ctx.req_of_token, table,
+                                    stride, s.window, s.scale, ctx.err, softcap=s.score_softcap,
+                                    slope_exponent=s.distance_slope_exponent, chunk=s.chunk)
+            return
         if bq <= 0 and not s.talking_heads and out_scale == 1.0 and out.is_contiguous():
             # no mix across heads: a head needs no other head in its block, and the kernel with one warp per
             # (token, head) takes any number of heads of any size (a silent entry of score 0 is a sink of zeros)
@@ -188,6 +223,8 @@ class TalkingAttention(Mixer):
         self.forward_inner(x, ctx, cache, state, writes_cache, inner, 1.0)
         out = ctx.workspace.get("tattn.out", (T, self.spec.hidden), ctx.branch_dtype or self.dtype)
         linear(out, inner, self.w_o, ctx.err)
+        if self.b_o is not None:
+            kernels.add_bias(out, self.b_o)
         return out
 
 
