@@ -184,11 +184,43 @@ def route(h, w_router, correction, top, groups, keep):
     return idx, s.gather(1, idx)
 
 
-def routed_experts(h, w, p, mlp, round_to=None):
+def follow_close_calls(h, w_router, correction, idx, wt, given, slack, groups=1, keep=1):
+    """An engine that rounds activations may decide a close call the other way.  ``given`` [T, top] are the experts
+    an engine chose: where a token's set differs from the plain one, every expert it took instead must have a
+    choice score within ``slack`` of one it left out (or belong to a group whose score is that close to a kept
+    group's) - else the engine's router is wrong and this raises.  Returns the engine's sets with their plain
+    scores as weights."""
+    s = torch.sigmoid(h @ w_router.T)
+    c = s + correction
+    out_i, out_w = idx.clone(), wt.clone()
+    T, E = c.shape
+    per = E // groups
+    gs = c.view(T, groups, per).topk(min(GROUP_BEST, per), dim=-1).values.sum(-1).sort(dim=-1, descending=True).values
+    for t in range(T):
+        mine, theirs = set(idx[t].tolist()), set(int(e) for e in given[t].tolist())
+        if mine == theirs:
+            continue
+        assert len(theirs) == len(mine), f"token {t}: the engine chose {sorted(theirs)}"
+        group_call = keep < groups and float(gs[t, keep - 1] - gs[t, keep]) <= 2 * slack
+        for e in theirs - mine:
+            if group_call:
+                continue
+            near = min(abs(float(c[t, e] - c[t, o])) for o in mine - theirs)
+            assert near <= slack, f"token {t}: expert {e} instead of one of {sorted(mine - theirs)} is no close call ({near:.3g})"
+        order = sorted(theirs, key=lambda e: -float(c[t, e]))
+        out_i[t] = torch.tensor(order)
+        out_w[t] = s[t, order]
+    return out_i, out_w
+
+
+def routed_experts(h, w, p, mlp, round_to=None, given=None, slack=0.0):
     r = mlp["router"]
     T = h.shape[0]
+    g = r.get("groups") or {"count": 1, "keep": 1}
     # the router reads h as the engine hands it over (possibly rounded); its own arithmetic stays wide
-    idx, wt = route(h, w[p + "router"], w[p + "correction"], r["top"], r["groups"]["count"], r["groups"]["keep"])
+    idx, wt = route(h, w[p + "router"], w[p + "correction"], r["top"], g["count"], g["keep"])
+    if given is not None:
+        idx, wt = follow_close_calls(h, w[p + "router"], w[p + "correction"], idx, wt, given, slack, g["count"], g["keep"])
     out = torch.zeros(T, w[p + "e0.down"].shape[0], dtype=F64)
     for t in range(T):
         for j in range(r["top"]):
@@ -199,10 +231,10 @@ def routed_experts(h, w, p, mlp, round_to=None):
     return out
 
 
-def feed_forward(h, w, p, mlp, round_to=None):
+def feed_forward(h, w, p, mlp, round_to=None, given=None, slack=0.0):
     if mlp["kind"] == "dense":
         return relu_feed_forward(h, w, p, round_to)
-    return routed_experts(h, w, p, mlp, round_to)
+    return routed_experts(h, w, p, mlp, round_to, given, slack)
 
 
 def layer_order(cfg):
@@ -218,16 +250,17 @@ def layer_order(cfg):
     return runs + [(i, False) for i in range(b, n)]
 
 
-def forward(cfg, w, tokens, round_to=None, streams=None):
+def forward(cfg, w, tokens, round_to=None, streams=None, routes=None, slack=0.0):
     """float64 logits [T, vocab] of one sequence; ``streams`` (a list) receives the residual stream after every
-    layer run."""
+    layer run.  ``routes``: per layer run (None where it has no router) the experts an engine chose, [T, top]: they
+    are followed where they differ from the plain choice by close calls only (``follow_close_calls``)."""
     tokens = torch.as_tensor(tokens, dtype=torch.int64)
     T = tokens.shape[0]
     positions = torch.arange(T)
     eps = cfg["norm"]["eps"]
     x0 = w["embed"][tokens]
     x = x0.clone()
-    for i, add_first in layer_order(cfg):
+    for run, (i, add_first) in enumerate(layer_order(cfg)):
         layer = cfg["layers"][i]
         p = f"l{i}."
         if add_first:
@@ -239,7 +272,8 @@ def forward(cfg, w, tokens, round_to=None, streams=None):
             a = capped_chunk_attention(h, w, p + "mix.", layer["mixer"], positions, round_to)
         else:
             raise ValueError(layer["type"])
-        f = feed_forward(h, w, p + "mlp.", layer["mlp"], round_to) if layer.get("mlp") is not None else 0.0
+        given = routes[run] if routes is not None else None
+        f = feed_forward(h, w, p + "mlp.", layer["mlp"], round_to, given, slack) if layer.get("mlp") is not None else 0.0
         x = x + (a + f)
         if streams is not None:
             streams.append(x.clone())

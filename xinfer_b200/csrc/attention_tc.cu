@@ -79,7 +79,7 @@ __device__ __forceinline__ PrefillItem prefill_item(const int* __restrict__ item
     w.t0 = q_start[b] + row0;
     w.p0 = start_pos[b] + row0;
     w.last_key = w.p0 + w.rows - 1;
-    w.first_key = window > 0 ? max(0, w.p0 - window + 1) : 0;
+    w.first_key = first_visible(w.p0, window);
     w.table = block_table + (size_t)b * table_stride;
     w.kt_first = w.first_key / KT;
     w.iters = w.last_key / KT - w.kt_first + 1;
@@ -94,8 +94,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ q_start, const int* __restrict__ start_pos,
                        const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d,
-                       int ps, int ps_shift, int num_pages, int window, float scale_log2,
+                       int ps, int ps_shift, int num_pages, int window, float scale_log2_in, float softcap, float slope_exp,
                        const int* __restrict__ work, int* err) {
+    // changed scores (a cap, a bias on the distance): the scores are brought to their final values first and the
+    // softmax then only changes the base of the exponential
+    const bool changed = softcap > 0.f || slope_exp > 0.f;
+    const float scale_nat = scale_log2_in * 0.6931471805599453f, inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    const float scale_log2 = changed ? 1.4426950408889634f : scale_log2_in;
     constexpr int HALVES = DP / 64, NS = PREFILL_STAGES;
     constexpr uint32_t Q_ONE = HALVES * QT * 128, Q_BYTES = 2 * Q_ONE;
     constexpr uint32_t KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF, STAGE_BYTES = 2 * KV_BYTES;
@@ -342,6 +347,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const int iters = w.iters, kt_first = w.kt_first, first_key = w.first_key, last_key = w.last_key, p0 = w.p0;
             const int rows = w.rows, t0 = w.t0, h0 = w.h0;
             const int my_pos = p0 + r;
+            const int my_lo = first_visible(my_pos, window), edge_lo = first_visible(p0 + QT - 1, window);
+            const float slope = head_slope(slope_exp, h0 + hd, nh);
             float m_ref = -INFINITY, l = 0.f;
             for (int it = 0; it < iters; ++it) {
                 const int th = Th + it, sb = th & 1, gt = T + it, st = gt % NS, key0 = (kt_first + it) * KT;
@@ -363,14 +370,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                         sc[32 + i] = __uint_as_float(rb[i]);
                     }
                 }
-                const bool edge = key0 + KT - 1 > p0 || key0 + KT - 1 > last_key || key0 < first_key ||
-                                  (window > 0 && key0 < p0 + QT - 1 - window + 1);
+                if (changed) {
+                    const float dist0 = (float)(my_pos - key0);
+    #pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        float v = sc[i] * scale_nat;
+                        if (softcap > 0.f) v = capped_score(v, softcap, inv_cap);
+                        sc[i] = fmaf(-slope, dist0 - (float)i, v);
+                    }
+                }
+                const bool edge = key0 + KT - 1 > p0 || key0 + KT - 1 > last_key || key0 < first_key || key0 < edge_lo;
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 if (edge) {
     #pragma unroll
                     for (int i = 0; i < 64; ++i) {
                         const int j = key0 + i;
-                        const bool ok = j <= my_pos && j <= last_key && (window <= 0 || j > my_pos - window);
+                        const bool ok = j <= my_pos && j <= last_key && j >= my_lo;
                         sc[i] = ok ? sc[i] : -INFINITY;
                     }
                 }
@@ -590,7 +605,7 @@ attn_decode_plan_kernel(int* __restrict__ plan, int capacity, const int* __restr
             const int t = small_token(z, q_start, num_entries, dec_max, direct);
             if (t >= 0 && req_of_token[t] >= 0) {
                 const int pos = positions[t];
-                const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+                const int lo = first_visible(pos, window);
                 tiles[i] = pos / KT - lo / KT + 1;
                 tok[i] = t;
             }
@@ -632,7 +647,7 @@ attn_decode_plan_kernel(int* __restrict__ plan, int capacity, const int* __restr
         const int cz = max(1, n / share);
         const int sz = (n + cz - 1) / cz, ns = (n + sz - 1) / sz;   // tiles per piece; pieces that hold any
         const int pos = positions[t];
-        const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const int lo = first_visible(pos, window);
         for (int j = 0; j < cz; ++j, ++at) {
             int where = at;
             if (sorted) {   // as many pieces are longer (or as long and earlier) as this one's place says
@@ -672,9 +687,14 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                       float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ plan,
                       const int* __restrict__ block_table, int table_stride, int nh, int nkv, int d, int ps,
-                      int ps_shift, int num_pages, float scale_log2, int dec_max, int splits_max, int page_cap,
-                      int* __restrict__ tickets, int* err) {
+                      int ps_shift, int num_pages, float scale_log2_in, float softcap, float slope_exp, int dec_max,
+                      int splits_max, int page_cap, int* __restrict__ tickets, int* err) {
     constexpr int HALVES = DP / 64, DEC_STAGES = dec_stages(DP);
+    // changed scores (a cap, a bias on the distance): brought to their final values before the softmax, which then
+    // only changes the base of the exponential
+    const bool changed = softcap > 0.f || slope_exp > 0.f;
+    const float scale_nat = scale_log2_in * 0.6931471805599453f, inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    const float scale_log2 = changed ? 1.4426950408889634f : scale_log2_in;
     constexpr uint32_t Q_HALF = DEC_ROWS * 128, Q_BYTES = HALVES * Q_HALF, P_ONE = DEC_ROWS * 128, P_BYTES = 2 * P_ONE;
     constexpr uint32_t KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF, STAGE_BYTES = 2 * KV_BYTES;
     constexpr uint32_t BAR_OFF = Q_BYTES + P_BYTES + DEC_STAGES * STAGE_BYTES;
@@ -853,11 +873,17 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if (set == 1 && !two) break;
                 float sc[16];
                 float mx2[2] = {-INFINITY, -INFINITY};   // over the raw scores: the scale is positive
+                const float slope = changed ? head_slope(slope_exp, h0 + r0 + 8 * set, nh) : 0.f;
 #pragma unroll
                 for (int k = 0; k < 8; ++k)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         float v = __uint_as_float(raw[4 * k + 2 * set + e]);
+                        if (changed) {
+                            v *= scale_nat;
+                            if (softcap > 0.f) v = capped_score(v, softcap, inv_cap);
+                            v = fmaf(-slope, (float)(pos - (key0 + 8 * k + 2 * quad + e)), v);
+                        }
                         if (edge) {
                             const int j = key0 + 8 * k + 2 * quad + e;
                             v = (j >= k_begin && j <= k_end) ? v : -INFINITY;
@@ -1093,7 +1119,8 @@ bool map_q3(CUtensorMap* out, const void* ptr, long long T, int nh, int d, int b
 template <int DP>
 int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo, void* out,
                    const int* q_start, const int* start_pos, const int* table, int stride, int nh, int nkv, int d, int ps,
-                   int ps_shift, int num_pages, int window, float sl2, const int* work, int ctas, int* err, cudaStream_t stream) {
+                   int ps_shift, int num_pages, int window, float sl2, float softcap, float slope_exp, const int* work, int ctas,
+                   int* err, cudaStream_t stream) {
     // Q of two heads, the key/value stages, the barriers' kilobyte, 4 KB of output staging per softmax warp and half
     constexpr size_t smem = 2 * (size_t)(DP / 64) * QT * 128 + PREFILL_STAGES * 2 * (size_t)(DP / 64) * KT * 128 + 1024 +
                             8 * (size_t)(DP / 64) * 4096;
@@ -1101,7 +1128,7 @@ int launch_prefill(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorM
     cudaFuncSetAttribute(attn_prefill_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     return xb_launch(attn_prefill_tc_kernel<DP>, dim3(ctas), dim3(PREFILL_THREADS), smem, stream, mq, mk, mv, mo,
                      (__nv_bfloat16*)out, q_start, start_pos, table, stride, nh, nkv, d, ps, ps_shift, num_pages,
-                     window, sl2, work, err);
+                     window, sl2, softcap, slope_exp, work, err);
 }
 
 constexpr int DEC_PAGE_CAP = 1024;   // block-table entries of a piece that are staged in shared memory
@@ -1109,15 +1136,15 @@ constexpr int DEC_PAGE_CAP = 1024;   // block-table entries of a piece that are 
 template <int DP>
 int launch_decode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, float* part_o,
                   float* part_ml, const int* plan, int pieces, const int* table, int stride, int nh, int nkv, int d, int ps,
-                  int ps_shift, int num_pages, float sl2, int dec_max, int splits_max, int* tickets, int overlap, int* err,
-                  cudaStream_t stream) {
+                  int ps_shift, int num_pages, float sl2, float softcap, float slope_exp, int dec_max, int splits_max,
+                  int* tickets, int overlap, int* err, cudaStream_t stream) {
     constexpr size_t smem = (size_t)(DP / 64) * DEC_ROWS * 128 + 2 * DEC_ROWS * 128 + dec_stages(DP) * 2 * (size_t)(DP / 64) * KT * 128 +
                             32 * dec_stages(DP) + 96 + (size_t)DEC_PAGE_CAP * 4;
     cudaFuncSetAttribute(attn_decode_tc_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(attn_decode_tc_kernel<DP>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     return xb_launch_opt(overlap != 0, attn_decode_tc_kernel<DP>, dim3(nkv, pieces), dim3(128), smem, stream, mq, mk, mv,
                          (__nv_bfloat16*)out, part_o, part_ml, plan, table, stride, nh, nkv, d, ps, ps_shift, num_pages, sl2,
-                         dec_max, splits_max, DEC_PAGE_CAP, tickets, err);
+                         softcap, slope_exp, dec_max, splits_max, DEC_PAGE_CAP, tickets, err);
 }
 
 }  // namespace
@@ -1129,8 +1156,8 @@ int launch_decode(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 // for a head size over 128 or not a multiple of 16, or a page size that is no power of two >= 8.
 XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const void* vc, const int* q_start,
                                  const int* start_pos, const int* table, int stride, int tokens,
-                                 int nh, int nkv, int d, int ps, int num_pages, int window, float scale,
-                                 const int* work, int ctas, int* err, cudaStream_t stream) {
+                                 int nh, int nkv, int d, int ps, int num_pages, int window, float scale, float softcap,
+                                 float slope_exp, const int* work, int ctas, int* err, cudaStream_t stream) {
     if (ctas <= 0) return 0;
     int shift = -1;
     for (int s = 3; s < 20; ++s)
@@ -1145,9 +1172,9 @@ XB_EXPORT int xb_attn_prefill_tc(void* out, const void* q, const void* kc, const
     const float sl2 = scale * 1.4426950408889634f;
     if (d <= 64)
         return launch_prefill<64>(mq, mk, mv, mo, out, q_start, start_pos, table, stride, nh, nkv, d, ps, shift, num_pages, window,
-                                  sl2, work, ctas, err, stream);
+                                  sl2, softcap, slope_exp, work, ctas, err, stream);
     return launch_prefill<128>(mq, mk, mv, mo, out, q_start, start_pos, table, stride, nh, nkv, d, ps, shift, num_pages, window,
-                               sl2, work, ctas, err, stream);
+                               sl2, softcap, slope_exp, work, ctas, err, stream);
 }
 // int32 a plan for `tokens` small tokens and `ctas` target CTAs must hold.
 XB_EXPORT long long xb_attn_decode_plan_size(int tokens, int ctas, int nkv) {
@@ -1184,8 +1211,8 @@ XB_EXPORT int xb_attn_decode_plan(int* plan, const int* positions, const int* re
 // 16, a page size that is no power of two >= 8, or more than 16 query heads per key/value head.
 XB_EXPORT int xb_attn_decode_tc(void* out, float* part_o, float* part_ml, const void* q, const void* kc, const void* vc,
                                 const int* plan, const int* table, int stride, int q_rows, int nh, int nkv, int d, int ps,
-                                int num_pages, float scale, int dec_max, int splits_max, int tokens, int ctas, int* tickets,
-                                int overlap, int* err, cudaStream_t stream) {
+                                int num_pages, float scale, float softcap, float slope_exp, int dec_max, int splits_max,
+                                int tokens, int ctas, int* tickets, int overlap, int* err, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     int shift = -1;
     for (int s = 3; s < 20; ++s)
@@ -1203,7 +1230,7 @@ XB_EXPORT int xb_attn_decode_tc(void* out, float* part_o, float* part_ml, const 
     const int pieces = tokens + ctas / nkv + 2;   // the most the plan can hold
     if (d <= 64)
         return launch_decode<64>(mq, mk, mv, out, part_o, part_ml, plan, pieces, table, stride, nh, nkv, d, ps, shift, num_pages,
-                                 sl2, dec_max, splits_max, tickets, overlap, err, stream);
+                                 sl2, softcap, slope_exp, dec_max, splits_max, tickets, overlap, err, stream);
     return launch_decode<128>(mq, mk, mv, out, part_o, part_ml, plan, pieces, table, stride, nh, nkv, d, ps, shift, num_pages,
-                              sl2, dec_max, splits_max, tickets, overlap, err, stream);
+                              sl2, softcap, slope_exp, dec_max, splits_max, tickets, overlap, err, stream);
 }

@@ -175,7 +175,9 @@ XB_API long long xb_attn_prefill_work(int B, const int* counts, const int* start
         if (n <= dec_max) continue;
         for (int ti = 0; ti * QT < n; ++ti) {
             const int p0 = starts[b] + ti * QT, rows = std::min(QT, n - ti * QT);
-            const int last_key = p0 + rows - 1, first_key = window > 0 ? std::max(0, p0 - window + 1) : 0;
+            // window > 0: a sliding window; window < 0: chunks of -window positions counted from position 0
+            const int last_key = p0 + rows - 1;
+            const int first_key = window > 0 ? std::max(0, p0 - window + 1) : (window < 0 ? p0 / (-window) * (-window) : 0);
             tiles.push_back({last_key / KT - first_key / KT + 1, b, ti});
         }
     }

@@ -429,6 +429,14 @@ def attn_tiled_supported(dtype, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
 
 
+def mask_code(window=None, chunk=None) -> int:
+    """The causal mask as the one number the tcgen05 attention kernels, their work list and their decode plan take:
+    0 every earlier key, w > 0 a sliding window of w keys, -c < 0 chunks of c positions counted from position 0."""
+    if window and chunk:
+        raise KernelError("a window and a chunked mask exclude each other")
+    return -int(chunk) if chunk else int(window or 0)
+
+
 def attn_prefill_queries(head_dim: int, warps: int = 8) -> int:
     """Queries one CTA of the prefill kernel takes (256-wide heads always use 4 warps)."""
     return 16 * (4 if head_dim > 128 else warps)
@@ -514,7 +522,8 @@ def attn_decode_plan(plan, positions, req_of_token, q_start, num_entries, window
 
 
 def attn_decode_tc(out, part_o, part_ml, q, k_cache, v_cache, plan, block_table, table_stride, scale, dec_max,
-                   splits_max, tokens, ctas, err, tickets=None, overlap: bool = True) -> bool:
+                   splits_max, tokens, ctas, err, tickets=None, overlap: bool = True, softcap=None,
+                   slope_exponent=None) -> bool:
     """The step's small tokens on tcgen05 tensor cores with TMA-fed pages, shared out as ``plan``
     says (``attn_decode_plan`` with the same tokens, ctas and kv heads).  A token and head in several
     pieces is merged through ``part_o`` / ``part_ml`` (float32, tokens*heads*splits_max*head_dim
@@ -522,7 +531,8 @@ def attn_decode_tc(out, part_o, part_ml, q, k_cache, v_cache, plan, block_table,
     zero); ``decode_tc_splits_max`` gives the ``splits_max`` that is always enough.  ``overlap``:
     start while the kernel before drains - only with a plan made before the step's first kernel.
     Returns False, having done nothing, for shapes the kernel does not take (a head size over
-    128, a page size that is no power of two >= 8, more than 16 query heads per key/value head)."""
+    128, a page size that is no power of two >= 8, more than 16 query heads per key/value head).
+    ``softcap`` / ``slope_exponent``: scores capped and biased by the distance as in ``attention_plain``."""
     T, nh, d = q.shape
     _need(q, "q", torch.bfloat16, (T, nh, d))
     _need(out, "out", torch.bfloat16, (T, nh, d))
@@ -545,7 +555,8 @@ def attn_decode_tc(out, part_o, part_ml, q, k_cache, v_cache, plan, block_table,
             raise KernelError("the attention ticket buffer is too small")
     rc = kernels_lib().xb_attn_decode_tc(
         out.data_ptr(), _ptr(part_o), _ptr(part_ml), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), plan.data_ptr(),
-        block_table.data_ptr(), int(table_stride), T, nh, nkv, d, ps, num_pages, float(scale), int(dec_max),
+        block_table.data_ptr(), int(table_stride), T, nh, nkv, d, ps, num_pages, float(scale), float(softcap or 0.0),
+        float(slope_exponent or 0.0), int(dec_max),
         int(splits_max), int(tokens), int(ctas), _ptr(tickets), int(bool(overlap)), err.data_ptr(), _stream())
     if rc == ERR_NOT_SUPPORTED:
         return False
@@ -658,12 +669,15 @@ def attn_prefill_work(counts, starts, dec_max: int, window, heads: int, kv_heads
     return host[:max(int(used), 1)], int(ctas.value)
 
 
-def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, block_table, table_stride, window, scale, work, ctas, err) -> bool:
+def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, block_table, table_stride, window, scale, work, ctas, err,
+                    softcap=None, slope_exponent=None) -> bool:
     """Prefill attention on tcgen05 (TMA-fed; scores, probabilities and accumulators in tensor memory):
     128 queries of two query heads of a key/value head per work item; ``work`` (int32, on the device)
     and ``ctas`` come from ``attn_prefill_work`` for the same step, heads and window.  Returns False,
     having done nothing, for sizes it does not take (head size over 128, page size not a power of two
-    from 8)."""
+    from 8).  ``window`` is a mask code here and in the work list and the decode plan: w > 0 a sliding window, -c < 0
+    chunks of c positions counted from the sequence's start (``mask_code``).  ``softcap`` / ``slope_exponent``: scores
+    capped and biased by the distance as in ``attention_plain``."""
     T, nh, d = q.shape
     _need(q, "q", torch.bfloat16, (T, nh, d))
     _need(out, "out", torch.bfloat16, (T, nh, d))
@@ -678,7 +692,7 @@ def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, block_table, t
     rc = kernels_lib().xb_attn_prefill_tc(
         out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), q_start.data_ptr(), start_pos.data_ptr(),
         block_table.data_ptr(), int(table_stride), T, nh, nkv, d, ps, num_pages, int(window or 0), float(scale),
-        work.data_ptr(), int(ctas), err.data_ptr(), _stream())
+        float(softcap or 0.0), float(slope_exponent or 0.0), work.data_ptr(), int(ctas), err.data_ptr(), _stream())
     if rc == ERR_NOT_SUPPORTED:
         return False
     _ok(rc, "attn_prefill_tc")

@@ -104,7 +104,7 @@ def _declare_kernels(lib):
     _sig(lib, "xb_qk_norm_rope_write_bf16", I,
          [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P])
     _sig(lib, "xb_swiglu_rows_bf16", I, [P, P, I, I, I, F, F, P])
-    _sig(lib, "xb_attn_prefill_tc", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P])
+    _sig(lib, "xb_attn_prefill_tc", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, P, I, P, P])
     _sig(lib, "xb_gemm_skinny_tc", I, [P, I, P, P, I, I, I, I, P, P])
     _sig(lib, "xb_gemm_skinny_swiglu", I, [P, P, P, I, I, I, I, P, P])
     _sig(lib, "xb_gemm_skinny_qkv", I,
@@ -149,4 +149,4 @@ def _declare_kernels(lib):
     _sig(lib, "xb_expert_gather", I, [I, P, P, P, P, I, I, I, I, P])
     _sig(lib, "xb_expert_combine", I, [I, P, P, P, I, I, I, P, P, P])
     _sig(lib, "xb_expert_router", I, [I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P])
-    _sig(lib, "xb_attn_decode_tc", I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, I, P, P])
+    _sig(lib, "xb_attn_decode_tc", I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, F, F, I, I, I, I, P, I, P, P])

@@ -178,19 +178,41 @@ def prepare_step(ctx, dtype, nh: int, nkv: int, d: int, page_size: int, window, 
             _prefill_work(ctx, nh, nkv, window)
 
 
-def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
+def takes_changed_scores(dtype, nh: int, nkv: int, d: int, page_size: int) -> bool:
+    """Capped scores, a distance bias and a chunked mask are built into the tcgen05 kernels only: whether they
+    take both the long portions and the single tokens of this layout."""
+    return (_enabled and PREFILL_TC and DECODE_TC and kernels.attn_tiled_supported(dtype, d)
+            and prefill_tc_takes(d, page_size) and decode_tc_takes(nh, nkv, d, page_size))
+
+
+def attend(out, q, cache, ctx, table, stride, window, scale, *, softcap=None, slope_exponent=None, chunk=None) -> None:
+    """``window``: a sliding window, or the mask code of ``kernels.mask_code`` (as ``prepare_step`` got it).
+    ``softcap`` / ``slope_exponent`` / ``chunk``: scores capped and biased by the distance, keys of the query's
+    own chunk only; these run on the tcgen05 kernels or, where those do not take the step, on the plain one."""
     T, nh, d = q.shape
     k_pages, v_pages = cache["k"], cache["v"]
-    if not (_enabled and kernels.attn_tiled_supported(q.dtype, d)):
+    changed = softcap is not None or slope_exponent is not None or chunk is not None
+    if chunk is not None:
+        window = kernels.mask_code(window, chunk)
+
+    def plain():
         kernels.attention_plain(out, q, k_pages, v_pages, ctx.positions, ctx.req_of_token, table, stride,
-                                window, scale, ctx.err)
+                                window if chunk is None else None, scale, ctx.err, softcap=softcap,
+                                slope_exponent=slope_exponent, chunk=chunk)
+
+    if not (_enabled and kernels.attn_tiled_supported(q.dtype, d)) or (
+            changed and not takes_changed_scores(q.dtype, nh, k_pages.shape[1], d, cache.page_size)):
+        plain()
         return
     plan = _plan(ctx, d)
     took = False
     if plan["tiles"] and PREFILL_TC and prefill_tc_takes(d, cache.page_size):
         work, ctas, _ = _prefill_work(ctx, nh, k_pages.shape[1], window)
         took = kernels.attn_prefill_tc(out, q, k_pages, v_pages, ctx.q_start, ctx.start_pos, table, stride, window, scale,
-                                       work, ctas, ctx.err)
+                                       work, ctas, ctx.err, softcap, slope_exponent)
+    if plan["tiles"] and not took and changed:
+        plain()         # (every token of the step, the small ones included)
+        return
     if plan["tiles"] and not took:
         kernels.attn_prefill_bf16(out, q, k_pages, v_pages, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride,
                                   window, scale, DEC_MAX, plan["tiles"], plan["prefill_bound"], ctx.err, warps=PREFILL_WARPS)
@@ -216,7 +238,12 @@ def attend(out, q, cache, ctx, table, stride, window, scale) -> None:
             buf, ctas, splits_max, overlap = planned
             scratch(splits_max)
             took = kernels.attn_decode_tc(out, part_o, part_ml, q, k_pages, v_pages, buf, table, stride, scale, DEC_MAX,
-                                          splits_max, small, ctas, ctx.err, tickets, overlap)
+                                          splits_max, small, ctas, ctx.err, tickets, overlap, softcap, slope_exponent)
+        if not took and changed:
+            if plan["tiles"]:
+                raise kernels.KernelError("a step of long portions and more single tokens than a plan takes, with changed scores")
+            plain()
+            return
         if not took:
             split, num_splits = decode_split(bound, small * nkv * ((nh // nkv + 15) // 16))
             scratch(num_splits)

@@ -123,7 +123,6 @@ class TalkingAttention(Mixer):
         ordinary grouped-query one, and the engine's tcgen05 kernels (work lists, decode plans) take it."""
         s = self.spec
         return (USE_ATTENTION_BACKEND and not s.talking_heads and not s.sink and s.value_dim == s.head_dim
-                and not self._changed_scores()
                 and self.dtype == torch.bfloat16 and kernels.attn_tiled_supported(self.dtype, s.head_dim))
 
     def _changed_scores(self) -> bool:
@@ -136,7 +135,7 @@ class TalkingAttention(Mixer):
             from . import attention_backend
             s = self.spec
             attention_backend.prepare_step(ctx, self.dtype, s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size,
-                                           s.window, ctx.strides[cache.group])
+                                           kernels.mask_code(s.window, s.chunk), ctx.strides[cache.group])
 
     # ---- the two halves ---------------------------------------------------------------------------
     def inner_width(self) -> int:
@@ -179,7 +178,8 @@ class TalkingAttention(Mixer):
         ws = ctx.workspace
         if self._plain_softmax() and out_scale == 1.0 and out.is_contiguous():
             from . import attention_backend
-            attention_backend.attend(out.view(T, nh, dv), q, cache, ctx, table, stride, s.window, s.scale)
+            attention_backend.attend(out.view(T, nh, dv), q, cache, ctx, table, stride, s.window, s.scale,
+                                     softcap=s.score_softcap, slope_exponent=s.distance_slope_exponent, chunk=s.chunk)
             return
         # queries per block: the longest portion decides (a step of single tokens takes one query per block
         # and cuts the keys instead); a replayed step must not look at its actual lengths
