@@ -9,6 +9,7 @@
     python bench.py --compare tidarax [--size 1k|4k]        # the Tidarax design beside Qwen3 at equal layer sizes
     python bench.py --compare dufitar [--size 1k|4k]        # the Dufitar design beside Qwen3 at equal layer sizes
     python bench.py --compare gulipel [--size 1k|4k]        # the Gulipel design beside Tidarax at equal layer sizes
+    python bench.py --compare mikutar [--size 1k|4k]        # the Mikutar design beside Dufitar at equal layer sizes
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and the context length
 of the configuration (a "step" is one decode step of the whole batch), timed on the device with
@@ -278,6 +279,25 @@ def gulipel_config(z: dict, layers: int, vocab: int, max_positions: int) -> dict
                 token_side=dict(dim=64), layers=out)
 
 
+# --compare mikutar: windowed attention / dense, windowed / experts, windowed / dense, chunked with capped scores /
+# experts; windows and chunks wider than the benchmark's context; experts of a quarter of the dense width in four
+# groups of which two are kept, beside an expert of the same size that every token runs.  ``loop``: the first three
+# layers run twice (seven layer runs) where it is set.
+def mikutar_config(z: dict, layers: int, vocab: int, loop: bool = False) -> dict:
+    d = z["head_dim"]
+    common = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, mask=dict(size=COMPARE_WINDOW))
+    attn = dict(type="attention", mixer=dict(common, rot=dict(dims=d // 2, base=250000.0)))
+    attn2 = dict(type="attention_2", mixer=dict(common, softcap=50.0))
+    dense = dict(kind="dense", ff=z["intermediate"])
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), shared=dict(ff=z["expert_ff"], limit=7.0),
+               router=dict(experts=z["experts"], top=z["top"], groups=dict(count=4, keep=2)))
+    out = [dict(attn2 if i % 4 == 3 else attn, mlp=moe if i % 2 else dense) for i in range(layers)]
+    cfg = dict(architecture="Mikutar", vocab=vocab, width=z["hidden"], norm=dict(eps=1e-6), logit_softcap=30.0, layers=out)
+    if loop and layers > 1:
+        cfg["loop"] = dict(start=0, stop=layers - 1, times=2)
+    return cfg
+
+
 def compare(args) -> int:
     """Prefill and decode throughput of a model of the named design and of a Qwen3 model of the same layer sizes
     (random weights, `--layers` layers each, default 4), then the design's kernels one by one beside their like
@@ -293,6 +313,9 @@ def compare(args) -> int:
                  num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"])
     if args.compare == "gulipel":       # its closest model is the other one with two mixers side by side
         models = {"Gulipel": gulipel_config(z, L, V, ctx_len + 128), "Tidarax": tidarax_config(z, L, V)}
+    elif args.compare == "mikutar":     # its closest model is the other one with gated window attention and a float32 stream
+        models = {"Mikutar": mikutar_config(z, L, V), "Mikutar, first layers twice": mikutar_config(z, L, V, loop=True),
+                  "Dufitar": dufitar_config(z, LATENT_SIZES[args.size], L, V)}
     elif args.compare == "tidarax":
         models = {"Tidarax": tidarax_config(z, L, V), "Qwen3": qwen3}
     else:
@@ -342,7 +365,11 @@ def compare(args) -> int:
                           "dtype": "bf16", "data": "synthetic (random weights, seeded uniform token ids)"}), flush=True)
         del runner
         torch.cuda.empty_cache()
-    if args.compare == "gulipel":
+    if args.compare == "mikutar":
+        records = measure.mikutar_kernels(hidden=z["hidden"], heads=z["heads"], kv_heads=z["kv_heads"], head_dim=z["head_dim"],
+                                          intermediate=z["intermediate"], experts=z["experts"], expert_ff=z["expert_ff"],
+                                          top=z["top"], hbm_gbs=pk["hbm_gbs"], peak_tflops=pk["bf16_tflops"])
+    elif args.compare == "gulipel":
         records = measure.gulipel_kernels(hidden=z["hidden"], heads=z["heads"], kv_heads=z["kv_heads"], head_dim=z["head_dim"],
                                           intermediate=z["intermediate"], hbm_gbs=pk["hbm_gbs"], **gulipel_sizes(z))
     elif args.compare == "dufitar":
@@ -383,7 +410,7 @@ def main() -> int:
                     help="with --kernels: the attention kernels alone at this head layout, over short and long contexts")
     ap.add_argument("--case", default="", metavar="decode:BATCHxCONTEXT | prefill:CACHED+NEW",
                     help="with --kernels --attn: this one case instead of the standard ones")
-    ap.add_argument("--compare", default="", choices=["", "tidarax", "dufitar", "gulipel"],
+    ap.add_argument("--compare", default="", choices=["", "tidarax", "dufitar", "gulipel", "mikutar"],
                     help="instead of the step benchmark: prefill and decode throughput of this design beside its closest model "
                          "(Qwen3; for gulipel, Tidarax) at equal layer sizes, and its kernels beside their like kernels; one JSON line each")
     ap.add_argument("--size", default="4k", choices=sorted(COMPARE_SIZES), help="layer sizes of --compare")

@@ -59,9 +59,12 @@ def _attention_context(entries, page_size: int, device):
 
 def decode_attention(cases: Sequence = ((1, 4096), (8, 4096), (64, 4096), (8, 32768)), *, heads: int = 32,
                      kv_heads: int = 8, head_dim: int = 128, page_size: int = 16, hbm_gbs: float = 0.0,
-                     device="cuda:0") -> List[Dict]:
-    """One decode token per request over `context` cached tokens, for (batch, context) cases."""
+                     device="cuda:0", softcap=None, slope_exponent=None, chunk=None) -> List[Dict]:
+    """One decode token per request over `context` cached tokens, for (batch, context) cases.  ``softcap``,
+    ``slope_exponent``, ``chunk``: the attention with capped scores, a distance bias and a chunked mask."""
     out = []
+    changes = dict(softcap=softcap, slope_exponent=slope_exponent, chunk=chunk)
+    mask = kernels.mask_code(None, chunk)
     for batch, context in cases:
         ctx, table, stride, num_pages = _attention_context([(context - 1, 1)] * batch, page_size, device)
         layers = 8 if batch * context <= 8 * 32768 else 2
@@ -77,9 +80,10 @@ def decode_attention(cases: Sequence = ((1, 4096), (8, 4096), (64, 4096), (8, 32
             try:
                 # as in a step: the work is planned once, before the first kernel, for all layers
                 ctx.scratch.clear()
-                attention_backend.prepare_step(ctx, torch.bfloat16, heads, kv_heads, head_dim, page_size, None, stride)
+                attention_backend.prepare_step(ctx, torch.bfloat16, heads, kv_heads, head_dim, page_size, mask, stride)
                 torch.cuda.synchronize()   # the launches below run on a stream of their own
-                rec[name] = round(_graph_time_us(lambda: [attention_backend.attend(o, q, c, ctx, table, stride, None, head_dim ** -0.5)
+                rec[name] = round(_graph_time_us(lambda: [attention_backend.attend(o, q, c, ctx, table, stride, None, head_dim ** -0.5,
+                                                                                   **changes)
                                                           for c in caches], layers), 1)
             finally:
                 attention_backend.DECODE_TC = True
@@ -93,9 +97,13 @@ def decode_attention(cases: Sequence = ((1, 4096), (8, 4096), (64, 4096), (8, 32
 
 
 def prefill_attention(cases: Sequence = ((0, 2048), (0, 8192), (24576, 8192)), *, heads: int = 32, kv_heads: int = 8,
-                      head_dim: int = 128, page_size: int = 16, peak_tflops: float = 0.0, device="cuda:0") -> List[Dict]:
-    """One request bringing `new` tokens after `cached` ones, for (cached, new) cases."""
+                      head_dim: int = 128, page_size: int = 16, peak_tflops: float = 0.0, device="cuda:0", softcap=None,
+                      slope_exponent=None, chunk=None) -> List[Dict]:
+    """One request bringing `new` tokens after `cached` ones, for (cached, new) cases.  ``softcap``,
+    ``slope_exponent``, ``chunk``: the attention with capped scores, a distance bias and a chunked mask."""
     out = []
+    changes = dict(softcap=softcap, slope_exponent=slope_exponent, chunk=chunk)
+    mask = kernels.mask_code(None, chunk)
     for cached, new in cases:
         ctx, table, stride, num_pages = _attention_context([(cached, new)], page_size, device)
         cache = LayerCache.of_keys_and_values(torch.randn(num_pages, kv_heads, page_size, head_dim, device=device).bfloat16(),
@@ -110,9 +118,10 @@ def prefill_attention(cases: Sequence = ((0, 2048), (0, 8192), (24576, 8192)), *
                 # several launches replayed from a CUDA graph: the host's share of a launch (tensor maps, wrappers)
                 # is not in the time, as it is not in a step, where launches queue ahead of the device
                 per = 4 if new * (cached + new) <= 8192 * 16384 else 1
-                attention_backend.prepare_step(ctx, torch.bfloat16, heads, kv_heads, head_dim, page_size, None, stride)
+                attention_backend.prepare_step(ctx, torch.bfloat16, heads, kv_heads, head_dim, page_size, mask, stride)
                 torch.cuda.synchronize()
-                rec[name] = round(_graph_time_us(lambda: [attention_backend.attend(o, q, cache, ctx, table, stride, None, head_dim ** -0.5)
+                rec[name] = round(_graph_time_us(lambda: [attention_backend.attend(o, q, cache, ctx, table, stride, None, head_dim ** -0.5,
+                                                                                   **changes)
                                                           for _ in range(per)], per), 1)
             finally:
                 attention_backend.PREFILL_TC = True
@@ -711,6 +720,110 @@ def gulipel_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
            lambda i: kernels.embed_sum(xs[i], table, ids, err, scale=4.0, pair=pair, pair_rule=(buckets, 31, 7), pos_table=pos,
                                        positions=positions, req_of_token=req, q_start=q_start, slots=slots, prev_state=prev),
            "embedding", tokens=T)
+    if int(err):
+        raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
+    return out
+
+
+def mikutar_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, head_dim: int = 128, intermediate: int = 12288,
+                    experts: int = 8, expert_ff: int = 3072, top: int = 2, groups: int = 4, keep: int = 2, softcap: float = 50.0,
+                    chunk: int = 4096, tokens: int = 2048, decode: Sequence[int] = (8, 4096), page_size: int = 16,
+                    hbm_gbs: float = 0.0, peak_tflops: float = 0.0, device="cuda:0") -> List[Dict]:
+    """One record per kernel of the Mikutar path: time, what it achieves and the share of its floor (bytes at the
+    measured copy rate, or tensor-core work at the measured matrix-product peak), each beside its like kernel.  The
+    windowed layers' attention IS the engine's tcgen05 kernel; the chunked layers run the same kernel with the
+    scores changed before the softmax, measured here beside the unchanged one."""
+    out: List[Dict] = []
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    bf = lambda *shape: torch.randn(*shape, device=device).bfloat16()
+    H, G, d = heads, kv_heads, head_dim
+    batch, context = decode
+    for name, kw in (("capped scores + distance bias + chunks", dict(softcap=softcap, slope_exponent=8.0, chunk=chunk)),
+                     ("distance bias + chunks, no cap", dict(slope_exponent=8.0, chunk=chunk)),
+                     ("like: the engine's attention, unchanged scores", {})):
+        rec = prefill_attention(((0, tokens),), heads=H, kv_heads=G, head_dim=d, page_size=page_size, peak_tflops=peak_tflops, **kw)[0]
+        out.append({"kernel": "prompt attention (tcgen05), " + name, "tokens": tokens, "us": rec["tcgen05_us"],
+                    "tensor_tflops": rec["tflops"], "frac_of_floor": rec.get("frac_of_peak")})
+        rec = decode_attention(((batch, context),), heads=H, kv_heads=G, head_dim=d, page_size=page_size, hbm_gbs=hbm_gbs, **kw)[0]
+        out.append({"kernel": "single-token attention (tcgen05), " + name, "batch": batch, "context": context,
+                    "us": rec["tcgen05_us"], "gbs": rec["gbs"], "frac_of_floor": rec.get("frac_of_hbm")})
+
+    sets = 4
+
+    def record(name, nbytes, run, like=None):
+        us = _graph_time_us(lambda: [run(i) for i in range(sets)], sets)
+        rec = {"kernel": name, "tokens": tokens, "bytes": nbytes, "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1)}
+        if hbm_gbs:
+            rec["frac_of_floor"] = round(rec["gbs"] / hbm_gbs, 3)
+        if like:
+            rec["like"] = like
+        out.append(rec)
+
+    # the float32 stream: the first branch by an addition kernel, the second with the norm that reads the sum
+    xs = [torch.randn(tokens, hidden, device=device) for _ in range(sets)]
+    bs = [torch.randn(tokens, hidden, device=device) for _ in range(sets)]
+    os_ = [torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    w = torch.randn(hidden, device=device)
+    record("float32 residual sum + RMS norm", tokens * hidden * (4 + 4 + 4 + 2),
+           lambda i: kernels.rmsnorm(os_[i], xs[i], w, 1e-6, err, branch=bs[i], sum_out=xs[i]), "residual sum + RMSNorm")
+    record("addition of a branch into the float32 stream", tokens * hidden * 12, lambda i: kernels.add(xs[i], xs[i], bs[i]),
+           "residual sum + RMSNorm")
+    del xs, bs, os_
+    # gates
+    gus = [bf(tokens, 2 * intermediate) for _ in range(sets)]
+    acts = [torch.empty(tokens, intermediate, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    record("ReLU gate", 3 * tokens * intermediate * 2, lambda i: kernels.swiglu(acts[i], gus[i], "relu"), "SiLU gate")
+    record("clamped swish gate", 3 * tokens * intermediate * 2,
+           lambda i: kernels.swiglu(acts[i], gus[i], "swish_clamp", (2.0, 1.702)), "SiLU gate")
+    del gus, acts
+    # one norm over the whole q and k projections, rotation of neighbours, keys as projected kept as values, page write
+    width = (H + G) * d + H
+    qkvs = [bf(tokens, width) for _ in range(sets)]
+    qs = [torch.empty(tokens, H, d, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    pages = (tokens + page_size - 1) // page_size
+    kcs = [torch.zeros(pages, G, page_size, d, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    vcs = [torch.zeros_like(k) for k in kcs]
+    inv = torch.rand(d // 2, device=device)
+    qw, kw_, bias = torch.randn(H * d, device=device), torch.randn(G * d, device=device), torch.randn((H + G) * d, device=device)
+    pos = torch.arange(tokens, dtype=torch.int32, device=device)
+    req = torch.zeros(tokens, dtype=torch.int32, device=device)
+    tab = torch.randperm(pages, device=device).to(torch.int32)
+    record("bias + norm over the whole projection + rotation + cache write of keys and raw keys", tokens * ((H + G) * d + (H + 2 * G) * d) * 2,
+           lambda i: kernels.qkv_prepare(qs[i], kcs[i], vcs[i], qkvs[i], qw, kw_, inv, pos, req, tab, pages, H, G, d, d, d, True, 3,
+                                         1e-6, True, err, bias=bias, row_len=width, value_offset=H * d),
+           "q/k norm + rotation + cache write")
+    inns = [bf(tokens, H * d) for _ in range(sets)]
+    record("sigmoid gate of one number per head (in place)", 2 * tokens * H * d * 2,
+           lambda i: kernels.gate_sigmoid(inns[i], inns[i].view(tokens, H, d).transpose(0, 1), qkvs[i][:, (H + G) * d:]), "SiLU gate")
+    del qkvs, qs, kcs, vcs, inns
+    # the router and the routed experts' kernels
+    hs = [bf(tokens, hidden) for _ in range(sets)]
+    wr, corr = torch.randn(experts, hidden, device=device) * hidden ** -0.5, torch.randn(experts, device=device) * 0.3
+    choice = torch.zeros(tokens, top, dtype=torch.int32, device=device)
+    weight = torch.zeros(tokens, top, dtype=torch.float32, device=device)
+    record("router: scores, choice among groups, weights", tokens * hidden * 2,
+           lambda i: kernels.expert_router(choice, weight, hs[i], wr, corr, req, top, groups, keep, 2), "residual sum + RMSNorm")
+    n = tokens * top
+    offsets = torch.zeros(experts + 1, dtype=torch.int32, device=device)
+    perm, inv_ = torch.zeros(n, dtype=torch.int32, device=device), torch.zeros(n, dtype=torch.int32, device=device)
+    kernels.expert_route(offsets, perm, inv_, choice, None, None, req, tokens, top, experts, err)
+    w_gu, w_dn = bf(experts, 2 * expert_ff, hidden) * 0.02, bf(hidden, experts * expert_ff) * 0.02
+    act = torch.empty(n, expert_ff, dtype=torch.bfloat16, device=device)
+    y = torch.empty(n, hidden, dtype=torch.float32, device=device)
+    for label, kw in (("clamped swish", dict(activation="swish_clamp", params=(2.0, 1.702))), ("like: SiLU", {})):
+        us = _loop_time_us(lambda: kernels.expert_gemm(act, hs[0], w_gu, offsets, perm, True, top, True, **kw))
+        fl = 2.0 * n * hidden * 2 * expert_ff
+        out.append({"kernel": f"experts, grouped gate/up product with the gate (mma.sync), {label}", "rows": n, "us": round(us, 1),
+                    "tensor_tflops": round(fl / us / 1e6, 1), "frac_of_floor": round(fl / us / 1e6 / (peak_tflops or 1590.0), 3)})
+    ys = [torch.randn(n, hidden, device=device) for _ in range(sets)]
+    outs = [torch.empty(tokens, hidden, device=device) for _ in range(sets)]
+    bases = [torch.randn(tokens, hidden, device=device) for _ in range(sets)]
+    record("experts, weighted sum of a token's experts onto the shared expert's result", tokens * hidden * 4 * (top + 2),
+           lambda i: kernels.expert_combine(outs[i], ys[i], inv_, top, weights=weight, base=bases[i]), "residual sum + RMSNorm")
+    for rec in prefill_elementwise(tokens, hidden=hidden, heads=H, kv_heads=G, head_dim=d, intermediate=intermediate,
+                                   page_size=page_size, hbm_gbs=hbm_gbs):
+        out.append({"kernel": "like: Qwen3 " + rec["kernel"], "tokens": tokens, "us": rec["us"], "gbs": rec["gbs"],
+                    "frac_of_floor": rec.get("frac_of_hbm")})
     if int(err):
         raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
     return out

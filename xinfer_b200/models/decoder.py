@@ -91,6 +91,9 @@ class DecoderModel:
                     total += t.numel() * t.element_size()
             for part in b.all_parts():
                 visit(part)
+                inner = getattr(part, "shared", None)
+                if inner is not None and hasattr(inner, "spec"):
+                    visit(inner)            # a feed-forward inside a mixture of experts holds its own weights
                 if getattr(getattr(part, "spec", None), "out_norms", None) is not None:
                     # two mixers side by side that keep their output projections apart hold their own weights
                     visit(part.left)
