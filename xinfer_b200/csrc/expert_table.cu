@@ -307,11 +307,38 @@ __global__ void expert_combine_kernel(TO* __restrict__ out, const float* __restr
     }
 }
 
+// the same with four columns per thread (N a multiple of 4, float32 out and base, 16-byte aligned rows): the same sums
+// in the same order
+__global__ void expert_combine4_kernel(float4* __restrict__ out, const float4* __restrict__ y, const int* __restrict__ inv,
+                                       int top, int N4, float weight, const float* __restrict__ weights,
+                                       const float4* __restrict__ base) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < N4; c += blockDim.x) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < top; ++k) {
+            const int r = inv[t * top + k];
+            if (r < 0) continue;
+            const float w = weights != nullptr ? weights[t * top + k] : 1.f;
+            const float4 v = y[(size_t)r * N4 + c];
+            s.x += w * v.x; s.y += w * v.y; s.z += w * v.z; s.w += w * v.w;
+        }
+        s.x *= weight; s.y *= weight; s.z *= weight; s.w *= weight;
+        if (base != nullptr) {
+            const float4 bv = base[(size_t)t * N4 + c];
+            s.x += bv.x; s.y += bv.y; s.z += bv.z; s.w += bv.w;
+        }
+        out[(size_t)t * N4 + c] = s;
+    }
+}
+
 XB_EXPORT int xb_expert_combine(int out_dtype, void* out, const float* y, const int* inv, int tokens, int top, int N,
                                 const float* weights, const void* base, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     const float weight = weights != nullptr ? 1.f : 1.f / (float)top;
-    if (out_dtype == XB_F32)
+    if (out_dtype == XB_F32 && N % 4 == 0 && !(((uintptr_t)out | (uintptr_t)y | (uintptr_t)base) & 15))
+        expert_combine4_kernel<<<tokens, 256, 0, stream>>>((float4*)out, (const float4*)y, inv, top, N / 4, weight, weights,
+                                                           (const float4*)base);
+    else if (out_dtype == XB_F32)
         expert_combine_kernel<float><<<tokens, 256, 0, stream>>>((float*)out, y, inv, top, N, weight, weights, (const float*)base);
     else
         expert_combine_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((__nv_bfloat16*)out, y, inv, top, N, weight, weights,

@@ -148,13 +148,20 @@ __global__ void gate_sigmoid_kernel(T* out, const T* heads, long long h_ts, long
 // grid (pieces of a token's row, tokens)
 __global__ void gate_sigmoid_bf16x8_kernel(__nv_bfloat16* out, const __nv_bfloat16* heads, long long h_ts,
                                            long long h_hs, const __nv_bfloat16* __restrict__ gate, long long g_ts, int nh,
-                                           int dv, int tokens) {
+                                           int dv, int tokens, int per_head) {
     const int w = nh * dv;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c >= w) return;
     const int h = c / dv, v = c - h * dv;
     for (int t = blockIdx.y; t < tokens; t += gridDim.y) {
-        const uint4 pg = *reinterpret_cast<const uint4*>(gate + (size_t)t * g_ts + c);
+        uint4 pg;
+        if (per_head) {     // one number for the head's eight channels
+            const unsigned short one = *reinterpret_cast<const unsigned short*>(gate + (size_t)t * g_ts + h);
+            const uint32_t two = (uint32_t)one | ((uint32_t)one << 16);
+            pg = make_uint4(two, two, two, two);
+        } else {
+            pg = *reinterpret_cast<const uint4*>(gate + (size_t)t * g_ts + c);
+        }
         const uint4 po = *reinterpret_cast<const uint4*>(heads + (size_t)t * h_ts + (size_t)h * h_hs + v);
         const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&pg);
         const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&po);
@@ -173,13 +180,13 @@ XB_EXPORT int xb_gate_sigmoid(int dtype, void* out, const void* heads, long long
                               long long g_ts, int tokens, int nh, int dv, int per_head, cudaStream_t stream) {
     const size_t n = (size_t)tokens * nh * dv;
     if (n == 0) return 0;
-    if (!per_head && dtype == XB_BF16 && dv % 8 == 0 && h_ts % 8 == 0 && h_hs % 8 == 0 && g_ts % 8 == 0 &&
-        !(((uintptr_t)out | (uintptr_t)heads | (uintptr_t)gate) & 15)) {
+    if (dtype == XB_BF16 && dv % 8 == 0 && h_ts % 8 == 0 && h_hs % 8 == 0 &&
+        !(((uintptr_t)out | (uintptr_t)heads) & 15) && (per_head || (g_ts % 8 == 0 && !((uintptr_t)gate & 15)))) {
         const int vecs = nh * dv / 8;
         const int threads = vecs >= 256 ? 256 : 64;
         const dim3 grid((unsigned)((vecs + threads - 1) / threads), (unsigned)(tokens < 65535 ? tokens : 65535));
         gate_sigmoid_bf16x8_kernel<<<grid, threads, 0, stream>>>(
-            (__nv_bfloat16*)out, (const __nv_bfloat16*)heads, h_ts, h_hs, (const __nv_bfloat16*)gate, g_ts, nh, dv, tokens);
+            (__nv_bfloat16*)out, (const __nv_bfloat16*)heads, h_ts, h_hs, (const __nv_bfloat16*)gate, g_ts, nh, dv, tokens, per_head);
         return xb_launch_status();
     }
     const unsigned blocks = (unsigned)((n + 255) / 256);

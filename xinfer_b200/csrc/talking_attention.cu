@@ -67,7 +67,7 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
                                    const float* __restrict__ bias, float temp_coef, int temp_every, long long row_len,
                                    long long v_off, int* err) {
     extern __shared__ float sm[];
-    __shared__ float red[33];
+    __shared__ float red2[2][32];
     const int half = rot / 2;
     float* cs = sm;                 // [half]
     float* sn = sm + half;          // [half]
@@ -99,12 +99,38 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
     float inv_q = 1.f, inv_k = 1.f;
     if (norm_mode == 3) {     // one root mean square over the whole q projection, one over the whole k projection
         float sq = 0.f, sk = 0.f;
-        for (int i = threadIdx.x; i < (nh + nkv) * d; i += blockDim.x) {
-            const float v = to_f32<T>(row[i]) + (bias ? bias[i] : 0.f);
-            if (i < nh * d) sq += v * v; else sk += v * v;
+        const int nq = nh * d, nqk = (nh + nkv) * d;
+        if (vec4) {           // (d a multiple of 4: a group of four never straddles q and k)
+            for (int i = threadIdx.x * 4; i < nqk; i += blockDim.x * 4) {
+                float v[4];
+                load4<T>(row + i, v);
+                float s4 = 0.f;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (bias) v[k] += bias[i + k];
+                    s4 += v[k] * v[k];
+                }
+                if (i < nq) sq += s4; else sk += s4;
+            }
+        } else {
+            for (int i = threadIdx.x; i < nqk; i += blockDim.x) {
+                const float v = to_f32<T>(row[i]) + (bias ? bias[i] : 0.f);
+                if (i < nq) sq += v * v; else sk += v * v;
+            }
         }
-        inv_q = 1.f / sqrtf(block_sum(sq, red) / (float)(nh * d) + eps);
-        inv_k = 1.f / sqrtf(block_sum(sk, red) / (float)(nkv * d) + eps);
+        // both sums through one pass over the block: an order fixed by the thread layout
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        if (lane == 0) {
+            red2[0][warp] = sq;
+            red2[1][warp] = sk;
+        }
+        __syncthreads();
+        float tq = lane < nwarps ? red2[0][lane] : 0.f, tk = lane < nwarps ? red2[1][lane] : 0.f;
+        tq = warp_sum(tq);
+        tk = warp_sum(tk);
+        inv_q = 1.f / sqrtf(tq / (float)nq + eps);
+        inv_k = 1.f / sqrtf(tk / (float)(nkv * d) + eps);
     }
     // the query's temperature: it grows with the logarithm of the number of whole periods the sequence has seen
     const float q_mul = temp_every > 0 ? 1.f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.f) : 1.f;
@@ -141,8 +167,49 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
                       : k_cache + (size_t)(kv_row + (long long)(h - nh) * page_size) * d;
         const float* nw = is_q ? q_w : k_w;
         if (norm_mode == 3 && nw) nw += (size_t)(is_q ? h : h - nh) * d;     // weights over the whole projection
+        if (vec4 && (norm_mode == 0 || norm_mode == 3) && (!inv_freq || (interleaved && rot % 4 == 0))) {
+            // nothing of a head is needed before its own elements can be finished (no norm over the head; pairs of
+            // neighbours lie in one group of four): load, bias, norm and weight, rotation, store - no shared memory
+            const float inv = norm_mode == 3 ? (is_q ? inv_q : inv_k) : 1.f;
+            for (int i = lane * 4; i < d; i += 128) {
+                float v[4];
+                load4<T>(x + i, v);
+                if (bh) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(bh + i);
+                    v[0] += b4.x; v[1] += b4.y; v[2] += b4.z; v[3] += b4.w;
+                }
+                if (norm_mode == 3) {
+                    float4 w4 = make_float4(1.f, 1.f, 1.f, 1.f);
+                    if (nw) w4 = *reinterpret_cast<const float4*>(nw + i);
+                    v[0] = v[0] * inv * w4.x; v[1] = v[1] * inv * w4.y; v[2] = v[2] * inv * w4.z; v[3] = v[3] * inv * w4.w;
+                }
+                if (inv_freq && i < rot) {
+                    const int j = i >> 1;
+                    const float u0 = v[0], w0 = v[1], u1 = v[2], w1 = v[3];
+                    v[0] = u0 * cs[j] - w0 * sn[j];
+                    v[1] = w0 * cs[j] + u0 * sn[j];
+                    v[2] = u1 * cs[j + 1] - w1 * sn[j + 1];
+                    v[3] = w1 * cs[j + 1] + u1 * sn[j + 1];
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v[k] *= om;
+                store4<T>(dst + i, v);
+            }
+            continue;
+        }
         float ss = 0.f;
-        if (vec4) {
+        if (vec4 && norm_mode == 3) {     // the root mean square is known already: norm and weight while loading
+            const float inv = is_q ? inv_q : inv_k;
+            for (int i = lane * 4; i < d; i += 128) {
+                float v[4];
+                load4<T>(x + i, v);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (bh) v[k] += bh[i + k];
+                    xs[i + k] = v[k] * inv * (nw ? nw[i + k] : 1.f);
+                }
+            }
+        } else if (vec4) {
             for (int i = lane * 4; i < d; i += 128) {
                 float v[4];
                 load4<T>(x + i, v);
@@ -161,7 +228,7 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
             }
         }
         __syncwarp();
-        if (norm_mode == 1 || norm_mode == 3) {
+        if (norm_mode == 1 || (norm_mode == 3 && !vec4)) {
             const float inv = norm_mode == 3 ? (is_q ? inv_q : inv_k) : 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
             for (int i = lane; i < d; i += 32) xs[i] = xs[i] * inv * (nw ? nw[i] : 1.f);
             __syncwarp();
@@ -217,6 +284,7 @@ XB_EXPORT int xb_qkv_prepare(int dtype, void* q_out, void* k_cache, void* v_cach
     // four elements per access where every head starts on such a boundary, in the rows and in the pages
     const size_t esz = dtype == XB_F32 ? 4 : 2;
     const int vec4 = (d % 4 == 0 && dv % 4 == 0 && row_len % 4 == 0 && v_off % 4 == 0 &&
+                      !(((uintptr_t)bias | (uintptr_t)q_w | (uintptr_t)k_w) & 15) &&
                       !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & (4 * esz - 1))) ? 1 : 0;
     if (dtype == XB_F32)
         qkv_prepare_kernel<float><<<tokens, threads, smem, stream>>>(
