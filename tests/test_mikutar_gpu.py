@@ -131,6 +131,18 @@ def test_routed_experts_part_equals_plain(dtype, T):
     want = plain.routed_experts(x.double(), w, "m.", mlp)
     keep = [t for t in range(T) if t != 1]
     assert (out[keep] - want[keep]).abs().max() <= (2e-5 if dtype == torch.float32 else 4e-2) * (1 + want.abs().max())
+    if dtype == torch.bfloat16 and T > 32:
+        # the form of large prompt steps: every expert's rows through the library's product
+        from xinfer_b200 import kernels
+        from xinfer_b200.parts import routed_experts as form
+        before, floor = kernels.launch_counts().get("expert_gather", 0), form.LIBRARY_FROM_FLOP_PER_CALL
+        form.LIBRARY_FROM_FLOP_PER_CALL = 0.0
+        try:
+            again = part.forward(x.to(DEV), ctx).double().cpu()
+        finally:
+            form.LIBRARY_FROM_FLOP_PER_CALL = floor
+        assert kernels.launch_counts().get("expert_gather", 0) == before + 1
+        assert (again[keep] - want[keep]).abs().max() <= 4e-2 * (1 + want.abs().max())
 
 
 # ---------------------------------------------------------------------------------------------

@@ -27,11 +27,14 @@ __host__ __device__ __forceinline__ int first_visible(int pos, int mask) {
 }
 
 // Scores that are changed before the softmax: s <- cap * tanh(s / cap) (cap > 0), then s <- s - slope * dist for a
-// key dist positions back.  tanh through one exponential and one quotient (absolute error about 1e-7).
-__device__ __forceinline__ float capped_score(float s, float cap, float inv_cap) {
-    float e;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(s * inv_cap * 2.8853900817779268f));   // e^(2 s / cap)
-    return cap * (1.f - __fdividef(2.f, e + 1.f));
+// key dist positions back.  With e = exp(2 s / cap), cap * tanh(s / cap) = cap - 2 cap / (e + 1): one exponential, one
+// reciprocal and one multiply-add that also takes whatever is added to the score (absolute error about 1e-7 of the
+// cap).  raw: the unscaled score; k1 = scale * 2 log2(e) / cap; base: cap plus what is added.
+__device__ __forceinline__ float capped_score(float raw, float k1, float neg2cap, float base) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(raw * k1));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));     // e = inf gives 0: the score is the cap
+    return fmaf(neg2cap, r, base);
 }
 // slope of head h of nh: 2^(-x (h + 1) / nh)
 __device__ __forceinline__ float head_slope(float x, int h, int nh) { return x > 0.f ? exp2f(-x * (float)(h + 1) / (float)nh) : 0.f; }

@@ -99,7 +99,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // changed scores (a cap, a bias on the distance): the scores are brought to their final values first and the
     // softmax then only changes the base of the exponential
     const bool changed = softcap > 0.f || slope_exp > 0.f;
-    const float scale_nat = scale_log2_in * 0.6931471805599453f, inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    const float scale_nat = scale_log2_in * 0.6931471805599453f;
+    const float cap_k1 = softcap > 0.f ? scale_nat * 2.8853900817779268f / softcap : 0.f, neg2cap = -2.f * softcap;
     const float scale_log2 = changed ? 1.4426950408889634f : scale_log2_in;
     constexpr int HALVES = DP / 64, NS = PREFILL_STAGES;
     constexpr uint32_t Q_ONE = HALVES * QT * 128, Q_BYTES = 2 * Q_ONE;
@@ -371,12 +372,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                 }
                 if (changed) {
-                    const float dist0 = (float)(my_pos - key0);
+                    // what is added to every score of the row in this tile: the bias of the tile's first key (and the cap)
+                    const float base = softcap - slope * (float)(my_pos - key0);
+                    if (softcap > 0.f) {
     #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        float v = sc[i] * scale_nat;
-                        if (softcap > 0.f) v = capped_score(v, softcap, inv_cap);
-                        sc[i] = fmaf(-slope, dist0 - (float)i, v);
+                        for (int i = 0; i < 64; ++i) sc[i] = fmaf(slope, (float)i, capped_score(sc[i], cap_k1, neg2cap, base));
+                    } else {
+    #pragma unroll
+                        for (int i = 0; i < 64; ++i) sc[i] = fmaf(slope, (float)i, fmaf(sc[i], scale_nat, base));
                     }
                 }
                 const bool edge = key0 + KT - 1 > p0 || key0 + KT - 1 > last_key || key0 < first_key || key0 < edge_lo;
@@ -693,7 +696,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     // changed scores (a cap, a bias on the distance): brought to their final values before the softmax, which then
     // only changes the base of the exponential
     const bool changed = softcap > 0.f || slope_exp > 0.f;
-    const float scale_nat = scale_log2_in * 0.6931471805599453f, inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    const float scale_nat = scale_log2_in * 0.6931471805599453f;
+    const float cap_k1 = softcap > 0.f ? scale_nat * 2.8853900817779268f / softcap : 0.f, neg2cap = -2.f * softcap;
     const float scale_log2 = changed ? 1.4426950408889634f : scale_log2_in;
     constexpr uint32_t Q_HALF = DEC_ROWS * 128, Q_BYTES = HALVES * Q_HALF, P_ONE = DEC_ROWS * 128, P_BYTES = 2 * P_ONE;
     constexpr uint32_t KV_HALF = KT * 128, KV_BYTES = HALVES * KV_HALF, STAGE_BYTES = 2 * KV_BYTES;
@@ -880,9 +884,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     for (int e = 0; e < 2; ++e) {
                         float v = __uint_as_float(raw[4 * k + 2 * set + e]);
                         if (changed) {
-                            v *= scale_nat;
-                            if (softcap > 0.f) v = capped_score(v, softcap, inv_cap);
-                            v = fmaf(-slope, (float)(pos - (key0 + 8 * k + 2 * quad + e)), v);
+                            const float base = softcap - slope * (float)(pos - key0 - 2 * quad);
+                            v = softcap > 0.f ? capped_score(v, cap_k1, neg2cap, base) : fmaf(v, scale_nat, base);
+                            v = fmaf(slope, (float)(8 * k + e), v);
                         }
                         if (edge) {
                             const int j = key0 + 8 * k + 2 * quad + e;

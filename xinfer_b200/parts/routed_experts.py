@@ -14,9 +14,13 @@ the table-driven experts (``parts/table_experts.py``) are reused with that table
   token's own experts (times their weights) and zeroes the others, ONE product with the down matrices side by side;
 * otherwise: the (token, choice) pairs are grouped by expert on the device, two grouped products run (gate/up with
   the activation applied in the same kernel, then down), and a last kernel sums a token's experts in the order of
-  its choices, each times its weight, onto the shared expert's result.
+  its choices, each times its weight, onto the shared expert's result;
+* large prompt steps in bfloat16: the grouping's offsets (one number per expert) are read back, and each expert's
+  contiguous rows go through the library's matrix product (gate/up, the gate kernel, down).  The read waits for the
+  device once per layer; where every product is large that costs far less than the grouped kernels lose to the
+  library's (about 200 against 1,400 TFLOP/s).
 
-Nothing comes back to the host: a step through this part can be replayed from a CUDA graph.
+Steps that are (or will be) replayed from a CUDA graph take the first two forms only: nothing comes back to the host.
 """
 from __future__ import annotations
 
@@ -33,6 +37,11 @@ from .linear import linear
 # up to this many tokens a bfloat16 step takes the dense form (all experts' matrices are read once, as they would be
 # anyway once most experts are in use)
 DENSE_MAX_TOKENS = 32
+# bfloat16 steps whose products are large enough go through per-expert library products (tests switch it off to reach
+# the grouped kernels); rows per expert are rounded up to ROW_STEP so that the library meets few distinct shapes
+PER_EXPERT_LIBRARY_PRODUCTS = True
+ROW_STEP = 128
+LIBRARY_FROM_FLOP_PER_CALL = 8e9
 
 
 class RoutedExperts(FeedForward):
@@ -111,11 +120,35 @@ class RoutedExperts(FeedForward):
         perm = ws.get("experts.perm", (n,), torch.int32)
         inv = ws.get("experts.inv", (n,), torch.int32)
         kernels.expert_route(offsets, perm, inv, choice, None, None, ctx.req_of_token, T, s.top, s.experts, ctx.err)
-        act = ws.get("experts.act", (n, s.intermediate), self.dtype)
-        y = ws.get("experts.y", (n, s.hidden), torch.float32)
-        kernels.expert_gemm(act, x, self.w_gate_up, offsets, perm, True, s.top, True, activation=s.activation,
-                            params=s.act_params)
-        kernels.expert_gemm(y, act, self.w_down, offsets, perm, False, s.top, False, side_by_side=True)
+        by_library = (PER_EXPERT_LIBRARY_PRODUCTS and self.dtype == torch.bfloat16 and not ctx.fixed_shapes
+                      and 6.0 * n * s.hidden * s.intermediate > LIBRARY_FROM_FLOP_PER_CALL * 3 * s.experts)
+        if by_library:
+            # Each expert's rows are rounded up to a multiple of ROW_STEP.  The extra rows are the next expert's: what
+            # is computed for them here is overwritten when that expert's turn comes, and past the last expert lies
+            # spare room that nobody reads.
+            bounds = offsets.cpu().tolist()         # (the one wait of this form)
+            room = n + ROW_STEP
+            act = ws.get("experts.act", (room, s.intermediate), self.dtype)
+            y = ws.get("experts.y", (room, s.hidden), torch.float32)
+            xp = ws.get("experts.x_grouped", (room, s.hidden), self.dtype)
+            kernels.expert_gather(xp[:n], x, perm, offsets, s.top)
+            gu = ws.get("experts.gate_up", (room, 2 * s.intermediate), self.dtype)
+            for e in range(s.experts):
+                at, c = bounds[e], bounds[e + 1] - bounds[e]
+                if c == 0:
+                    continue
+                m = min((c + ROW_STEP - 1) // ROW_STEP * ROW_STEP, room - at)
+                torch.mm(xp[at:at + m], self.w_gate_up[e].t(), out=gu[at:at + m])
+                kernels.swiglu(act[at:at + m], gu[at:at + m], s.activation, s.act_params)
+                torch.mm(act[at:at + m], self.w_down[:, e * s.intermediate:(e + 1) * s.intermediate].t(),
+                         out_dtype=torch.float32, out=y[at:at + m])
+            y = y[:n]
+        else:
+            act = ws.get("experts.act", (n, s.intermediate), self.dtype)
+            y = ws.get("experts.y", (n, s.hidden), torch.float32)
+            kernels.expert_gemm(act, x, self.w_gate_up, offsets, perm, True, s.top, True, activation=s.activation,
+                                params=s.act_params)
+            kernels.expert_gemm(y, act, self.w_down, offsets, perm, False, s.top, False, side_by_side=True)
         kernels.expert_combine(out, y, inv, s.top, weights=weight, base=base)
         return out
 
