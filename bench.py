@@ -275,7 +275,7 @@ def gulipel_config(z: dict, layers: int, vocab: int, max_positions: int) -> dict
     out = [dict(type="parallel", mixer=par, mlp=dense) if i % 2 == 1 else dict(type="mamba2" if i % 4 == 0 else "mamba2_2", mixer=ssm, mlp=dense)
            for i in range(layers)]
     return dict(architecture="Gulipel", vocab=vocab, width=z["hidden"], norm=dict(eps=1e-6), max_positions=max_positions,
-                logit_softcap=50.0, embedding=dict(scale=z["hidden"] ** 0.5, bigram=dict(buckets=100003, mul_prev=8191, mul_cur=31)),
+                logit_softcap=40.0, embedding=dict(scale=z["hidden"] ** 0.5, bigram=dict(buckets=100003, mul_prev=8191, mul_cur=31)),
                 token_side=dict(dim=64), layers=out)
 
 
@@ -286,8 +286,8 @@ def gulipel_config(z: dict, layers: int, vocab: int, max_positions: int) -> dict
 def mikutar_config(z: dict, layers: int, vocab: int, loop: bool = False) -> dict:
     d = z["head_dim"]
     common = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, mask=dict(size=COMPARE_WINDOW))
-    attn = dict(type="attention", mixer=dict(common, rot=dict(dims=d // 2, base=250000.0)))
-    attn2 = dict(type="attention_2", mixer=dict(common, softcap=50.0))
+    attn = dict(type="attention", mixer=dict(common, rot=dict(dims=d // 2, base=500000.0)))
+    attn2 = dict(type="attention_2", mixer=dict(common, softcap=40.0))
     dense = dict(kind="dense", ff=z["intermediate"])
     moe = dict(kind="moe", expert=dict(ff=z["expert_ff"], limit=7.0), shared=dict(ff=z["expert_ff"], limit=7.0),
                router=dict(experts=z["experts"], top=z["top"], groups=dict(count=4, keep=2)))

@@ -65,7 +65,7 @@ TINY_M: Dict[str, tuple] = {
     "M3": (dict(architecture="Mikutar", vocab=120, width=96, norm=dict(eps=1e-6), layers=[
         _moe(_attn(6, 3, 16, 0.45, 130, dict(dims=16, base=20000.0)), 48, 1.0, 5, 2),
         _dense(_attn2(3, 1, 48, 48, 0.2, 32, 5.0), 128),
-        _none(_attn2(6, 6, 16, 16, 0.7, 7, 50.0)),
+        _none(_attn2(6, 6, 16, 16, 0.7, 7, 45.0)),
     ]), 33, 32),
     # a loop over one layer that is also the last, one pass "loop", a width that is no multiple of 8
     "M4": (dict(architecture="Mikutar", vocab=61, width=52, norm=dict(eps=2e-6), logit_softcap=4.0,

@@ -726,7 +726,7 @@ def gulipel_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
 
 
 def mikutar_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, head_dim: int = 128, intermediate: int = 12288,
-                    experts: int = 8, expert_ff: int = 3072, top: int = 2, groups: int = 4, keep: int = 2, softcap: float = 50.0,
+                    experts: int = 8, expert_ff: int = 3072, top: int = 2, groups: int = 4, keep: int = 2, softcap: float = 40.0,
                     chunk: int = 4096, tokens: int = 2048, decode: Sequence[int] = (8, 4096), page_size: int = 16,
                     hbm_gbs: float = 0.0, peak_tflops: float = 0.0, device="cuda:0") -> List[Dict]:
     """One record per kernel of the Mikutar path: time, what it achieves and the share of its floor (bytes at the
